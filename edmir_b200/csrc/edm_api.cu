@@ -1,0 +1,508 @@
+// C ABI over the fused tensor-parallel GEMM kernel: argument checks, tensor-map encoding,
+// symmetric-memory contexts and launches.  No torch types, no allocation on the launch path.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/edm_b200.h"
+#include "tp_gemm.cuh"
+
+using namespace edm;
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+uint64_t g_timeout_ns = 2000ull * 1000ull * 1000ull;
+
+#define EDM_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t e__ = (expr);                            \
+    if (e__ != cudaSuccess) {                            \
+      g_last_cuda_error = static_cast<int>(e__);         \
+      return EDM_ERR_CUDA;                               \
+    }                                                    \
+  } while (0)
+
+// ---- driver entry point for tensor-map encoding (no link against libcuda) -------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// K-major matrix [rows, k] with leading dimension ld (elements); box = 128 bytes of K x box_rows.
+int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes,
+              int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return EDM_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * elem_bytes) & 15)) return EDM_ERR_BAD_ARG;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstr[1] = {static_cast<cuuint64_t>(ld * elem_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockKBytes / elem_bytes),
+                       static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = 100000 + static_cast<int>(r);
+    return EDM_ERR_CUDA;
+  }
+  return EDM_OK;
+}
+
+int num_sms() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return n;
+}
+
+template <bool kTf32, typename OutT>
+int launch_kernel(const LaunchParams& lp, int grid, bool cooperative, cudaStream_t stream) {
+  auto kern = tp_gemm_kernel<kTf32, OutT>;
+  static bool configured = false;  // one flag per instantiation
+  if (!configured) {
+    EDM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured = true;
+  }
+  if (cooperative) {
+    void* args[1] = {const_cast<LaunchParams*>(&lp)};
+    EDM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), dim3(grid), dim3(kThreads),
+                                         args, kSmemBytes, stream));
+  } else {
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(lp);
+    EDM_CUDA(cudaGetLastError());
+  }
+  return EDM_OK;
+}
+
+int launch_dtype(int dtype, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
+  if (dtype == EDM_DTYPE_BF16) return launch_kernel<false, __nv_bfloat16>(lp, grid, coop, stream);
+  return launch_kernel<true, float>(lp, grid, coop, stream);
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t split_ws_bytes(int64_t M, int64_t N, int64_t K) {
+  return 2 * (align_up(static_cast<size_t>(M) * K * 4, 256) + align_up(static_cast<size_t>(N) * K * 4, 256));
+}
+
+// Fills tmap_a/tmap_b (and runs the tf32 split for fp32) for a GEMM A[M,K] x B[N,K].
+int prepare_operands(RankParams& P, int dtype, const void* a, int64_t lda, int64_t a_rows,
+                     const void* b, int64_t ldb, int64_t N, int64_t K, void* ws, size_t ws_bytes,
+                     cudaStream_t stream) {
+  if (dtype == EDM_DTYPE_BF16) {
+    if (K % 8 || N % 8) return EDM_ERR_BAD_ARG;
+    int rc = make_tmap(&P.tmap_a[0], a, a_rows, K, lda, 2, kBlockM);
+    if (rc) return rc;
+    P.tmap_a[1] = P.tmap_a[0];
+    rc = make_tmap(&P.tmap_b[0], b, N, K, ldb, 2, kBlockN);
+    if (rc) return rc;
+    P.tmap_b[1] = P.tmap_b[0];
+    P.passes = 1;
+    return EDM_OK;
+  }
+  if (dtype != EDM_DTYPE_FP32) return EDM_ERR_BAD_ARG;
+  if (K % 4 || N % 4) return EDM_ERR_BAD_ARG;
+  if (!ws || ws_bytes < split_ws_bytes(a_rows, N, K)) return EDM_ERR_CAPACITY;
+  if (reinterpret_cast<uintptr_t>(ws) & 255u) return EDM_ERR_BAD_ARG;
+  char* w = static_cast<char*>(ws);
+  const size_t a_sz = align_up(static_cast<size_t>(a_rows) * K * 4, 256);
+  const size_t b_sz = align_up(static_cast<size_t>(N) * K * 4, 256);
+  float* a_hi = reinterpret_cast<float*>(w);
+  float* a_lo = reinterpret_cast<float*>(w + a_sz);
+  float* b_hi = reinterpret_cast<float*>(w + 2 * a_sz);
+  float* b_lo = reinterpret_cast<float*>(w + 2 * a_sz + b_sz);
+  split_tf32_kernel<<<296, 256, 0, stream>>>(static_cast<const float*>(a), a_hi, a_lo, a_rows, K, lda);
+  split_tf32_kernel<<<296, 256, 0, stream>>>(static_cast<const float*>(b), b_hi, b_lo, N, K, ldb);
+  EDM_CUDA(cudaGetLastError());
+  int rc;
+  if ((rc = make_tmap(&P.tmap_a[0], a_hi, a_rows, K, K, 4, kBlockM))) return rc;
+  if ((rc = make_tmap(&P.tmap_a[1], a_lo, a_rows, K, K, 4, kBlockM))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN))) return rc;
+  P.passes = 3;
+  return EDM_OK;
+}
+
+int check_dims(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return EDM_ERR_BAD_ARG;
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return EDM_ERR_BAD_ARG;
+  return EDM_OK;
+}
+
+int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+               int64_t M, int64_t N, int64_t K, void* ws, size_t ws_bytes, void* stream) {
+  if (!a || !b || !d) return EDM_ERR_BAD_ARG;
+  int rc = check_dims(M, N, K);
+  if (rc) return rc;
+  const int out_bytes = dtype == EDM_DTYPE_BF16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(d) & 15u) || ((ldd * out_bytes) & 15) || ldd < N) return EDM_ERR_BAD_ARG;
+  if (lda < K || ldb < K) return EDM_ERR_BAD_ARG;
+  LaunchParams lp;
+  std::memset(&lp, 0, sizeof(lp));
+  RankParams& P = lp.r[0];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = prepare_operands(P, dtype, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
+  if (rc) return rc;
+  P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
+  P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
+  P.out = d; P.ld_out = ldd;
+  const int tiles = static_cast<int>(((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN));
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  const int grid = tiles < sms ? tiles : sms;
+  lp.num_vranks = 1;
+  lp.ctas_per_vrank = grid;
+  lp.timeout_ns = g_timeout_ns;
+  return launch_dtype(dtype, lp, grid, false, s);
+}
+
+}  // namespace
+
+// ======================================================================== contexts
+struct edm_comm {
+  int rank = 0, world = 1;
+  int device = 0;
+  char* base[EDM_MAX_RANKS] = {};  // every rank's allocation as mapped in this process
+  bool imported[EDM_MAX_RANKS] = {};
+  size_t flag_bytes = 0;     // both parities
+  size_t counter_bytes = 0;
+  size_t window_bytes = 0;   // both parities
+  size_t heap_bytes = 0;
+  size_t heap_used = 0;
+  size_t total_bytes = 0;
+  uint32_t epoch = 0;
+
+  size_t off_flags() const { return 0; }
+  size_t off_counters() const { return flag_bytes; }
+  size_t off_window() const { return flag_bytes + counter_bytes; }
+  size_t off_heap() const { return flag_bytes + counter_bytes + window_bytes; }
+};
+
+namespace {
+constexpr size_t kFlagBytesPerParity = 2u << 20;  // 512 Ki flag words per parity
+constexpr size_t kCounterBytes = 64u << 10;
+
+struct Layout {
+  int64_t m_blocks, n_blocks, total;
+  int32_t max_owned = 0;
+  uint32_t partial_off = 0, result_off = 0, gather_off = 0, flag_words = 0;
+  size_t window_need = 0;
+};
+
+int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int elem_bytes, Layout& L) {
+  const int W = c->world;
+  L.m_blocks = (call.M + kBlockM - 1) / kBlockM;
+  L.n_blocks = (call.N + kBlockN - 1) / kBlockN;
+  L.total = L.m_blocks * L.n_blocks;
+  if (L.total > (1 << 24)) return EDM_ERR_BAD_ARG;
+  const size_t tile_bytes = static_cast<size_t>(kBlockM) * kBlockN * out_bytes;
+  if (call.op == EDM_OP_GEMM_RS) {
+    if (call.M % W) return EDM_ERR_BAD_ARG;
+    const int64_t rows = call.M / W;
+    if (rows % kBlockM) return EDM_ERR_UNSUPPORTED;  // row blocks must not straddle owners
+    L.max_owned = static_cast<int32_t>(rows / kBlockM * L.n_blocks);
+    L.window_need = tile_bytes * L.max_owned * W;
+    L.flag_words = static_cast<uint32_t>(W) * L.max_owned * 4;
+  } else if (call.op == EDM_OP_GEMM_AR) {
+    L.max_owned = static_cast<int32_t>((L.total + W - 1) / W);
+    L.window_need = tile_bytes * L.max_owned * W;
+    L.partial_off = 0;
+    L.result_off = static_cast<uint32_t>(W) * L.max_owned * 4;
+    L.flag_words = L.result_off + static_cast<uint32_t>(L.total) * 4;
+  } else if (call.op == EDM_OP_AG_GEMM) {
+    if (call.M % W || call.chunks < 1 || call.chunks > 4096 || call.chunks > call.M / W)
+      return EDM_ERR_BAD_ARG;
+    L.window_need = static_cast<size_t>(call.M) * call.K * elem_bytes;
+    L.gather_off = 0;
+    L.flag_words = static_cast<uint32_t>(W) * call.chunks;
+    if (static_cast<size_t>(W) * call.chunks * 4 > c->counter_bytes) return EDM_ERR_CAPACITY;
+  } else {
+    return EDM_ERR_BAD_ARG;
+  }
+  if (L.window_need > c->window_bytes / 2) return EDM_ERR_CAPACITY;
+  if (static_cast<size_t>(L.flag_words) * 4 > c->flag_bytes / 2) return EDM_ERR_CAPACITY;
+  return EDM_OK;
+}
+
+// Builds one rank's kernel parameters; bumps the context epoch.
+int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cudaStream_t stream) {
+  if (!c || !call.a || !call.b || !call.d) return EDM_ERR_BAD_ARG;
+  int rc = check_dims(call.M, call.N, call.K);
+  if (rc) return rc;
+  const int W = c->world;
+  for (int p = 0; p < W; ++p)
+    if (!c->base[p]) return EDM_ERR_BAD_ARG;  // peers not linked yet
+  const int elem_bytes = call.dtype == EDM_DTYPE_BF16 ? 2 : 4;
+  const int out_bytes = elem_bytes;
+  if (call.dtype != EDM_DTYPE_BF16 && call.dtype != EDM_DTYPE_FP32) return EDM_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(call.d) & 15u) || ((call.ldd * out_bytes) & 15) || call.ldd < call.N)
+    return EDM_ERR_BAD_ARG;
+  if (call.lda < call.K || call.ldb < call.K) return EDM_ERR_BAD_ARG;
+
+  std::memset(&P, 0, sizeof(P));
+  P.M = static_cast<int32_t>(call.M); P.N = static_cast<int32_t>(call.N); P.K = static_cast<int32_t>(call.K);
+  P.rank = c->rank; P.world = W;
+  P.out = call.d; P.ld_out = call.ldd;
+
+  if (W == 1 || call.op == EDM_OP_GEMM) {
+    // a one-rank group needs no exchange
+    if (call.op == EDM_OP_GEMM_AR || call.op == EDM_OP_GEMM_RS || call.op == EDM_OP_GEMM ||
+        call.op == EDM_OP_AG_GEMM) {
+      P.mode = kPlain; P.epoch = 1;
+      return prepare_operands(P, call.dtype, call.a, call.lda, call.M, call.b, call.ldb, call.N,
+                              call.K, call.workspace, call.workspace_bytes, stream);
+    }
+    return EDM_ERR_BAD_ARG;
+  }
+
+  Layout L;
+  rc = plan_layout(c, call, out_bytes, elem_bytes, L);
+  if (rc) return rc;
+
+  const uint32_t epoch = c->epoch + 1;
+  const size_t par = epoch & 1u;
+  for (int p = 0; p < W; ++p) {
+    P.flags[p] = reinterpret_cast<uint32_t*>(c->base[p] + c->off_flags() + par * (c->flag_bytes / 2));
+    P.win[p] = c->base[p] + c->off_window() + par * (c->window_bytes / 2);
+    P.gather[p] = P.win[p];
+  }
+  P.counters = reinterpret_cast<uint32_t*>(c->base[c->rank] + c->off_counters());
+  P.epoch = epoch;
+  P.max_owned = L.max_owned;
+  P.partial_flag_off = L.partial_off;
+  P.result_flag_off = L.result_off;
+  P.gather_flag_off = L.gather_off;
+
+  if (call.op == EDM_OP_AG_GEMM) {
+    if (call.dtype != EDM_DTYPE_BF16) return EDM_ERR_UNSUPPORTED;
+    if (call.K % 8 || call.N % 8) return EDM_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(call.a) & 15u || (call.lda * 2) & 15) return EDM_ERR_BAD_ARG;
+    const int64_t rows = call.M / W;
+    P.mode = kAG;
+    P.ag_chunks = call.chunks;
+    P.ag_local_direct = (rows % kBlockM == 0) ? 1 : 0;
+    P.x_local = call.a; P.ld_x = call.lda;
+    P.passes = 1;
+    // A comes from the local gather buffer [M,K]; the own shard is read in place when it
+    // covers whole row blocks
+    if ((rc = make_tmap(&P.tmap_a[0], P.gather[c->rank], call.M, call.K, call.K, 2, kBlockM))) return rc;
+    if ((rc = make_tmap(&P.tmap_a[1], call.a, rows, call.K, call.lda, 2, kBlockM))) return rc;
+    if ((rc = make_tmap(&P.tmap_b[0], call.b, call.N, call.K, call.ldb, 2, kBlockN))) return rc;
+    P.tmap_b[1] = P.tmap_b[0];
+  } else {
+    P.mode = call.op == EDM_OP_GEMM_RS ? kRS : kAR;
+    if (call.op == EDM_OP_GEMM_AR) {
+      // peers store reduced tiles straight into this tensor: it must sit in the symmetric heap
+      const char* d = static_cast<const char*>(call.d);
+      const char* heap0 = c->base[c->rank] + c->off_heap();
+      const size_t span = (static_cast<size_t>(call.M - 1) * call.ldd + call.N) * out_bytes;
+      if (d < heap0 || d + span > heap0 + c->heap_bytes) return EDM_ERR_NOT_SYMMETRIC;
+      const size_t off = static_cast<size_t>(d - c->base[c->rank]);
+      for (int p = 0; p < W; ++p) P.peer_out[p] = c->base[p] + off;
+    }
+    rc = prepare_operands(P, call.dtype, call.a, call.lda, call.M, call.b, call.ldb, call.N, call.K,
+                          call.workspace, call.workspace_bytes, stream);
+    if (rc) return rc;
+  }
+  c->epoch = epoch;
+  return EDM_OK;
+}
+
+int grid_for(const RankParams& P, int sms) {
+  if (P.mode == kAG) return sms;  // push warps of every CTA help move the shard
+  const int tiles = ((P.M + kBlockM - 1) / kBlockM) * ((P.N + kBlockN - 1) / kBlockN);
+  return tiles < sms ? tiles : sms;
+}
+}  // namespace
+
+extern "C" {
+
+int edm_version(void) { return 1; }
+int edm_last_cuda_error(void) { return g_last_cuda_error; }
+
+int edm_status_read(uint32_t out[16]) {
+  if (!out) return EDM_ERR_BAD_ARG;
+  EDM_CUDA(cudaDeviceSynchronize());
+  EDM_CUDA(cudaMemcpyFromSymbol(out, g_status, sizeof(uint32_t) * 16));
+  return EDM_OK;
+}
+int edm_status_clear(void) {
+  uint32_t z[16] = {};
+  EDM_CUDA(cudaDeviceSynchronize());
+  EDM_CUDA(cudaMemcpyToSymbol(g_status, z, sizeof(z)));
+  return EDM_OK;
+}
+int edm_set_timeout_ms(uint32_t ms) {
+  if (ms == 0) return EDM_ERR_BAD_ARG;
+  g_timeout_ns = static_cast<uint64_t>(ms) * 1000000ull;
+  return EDM_OK;
+}
+
+int edm_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+                  int64_t M, int64_t N, int64_t K, void* stream) {
+  return plain_gemm(EDM_DTYPE_BF16, a, lda, b, ldb, d, ldd, M, N, K, nullptr, 0, stream);
+}
+
+size_t edm_gemm_fp32_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return split_ws_bytes(M, N, K);
+}
+int edm_gemm_fp32(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+                  int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  return plain_gemm(EDM_DTYPE_FP32, a, lda, b, ldb, d, ldd, M, N, K, workspace, workspace_bytes, stream);
+}
+
+int edm_comm_create(int rank, int world, size_t window_bytes, size_t heap_bytes, edm_comm_t** out) {
+  if (!out || world < 1 || world > EDM_MAX_RANKS || rank < 0 || rank >= world) return EDM_ERR_BAD_ARG;
+  edm_comm* c = new (std::nothrow) edm_comm();
+  if (!c) return EDM_ERR_CAPACITY;
+  c->rank = rank; c->world = world;
+  EDM_CUDA(cudaGetDevice(&c->device));
+  c->flag_bytes = 2 * kFlagBytesPerParity;
+  c->counter_bytes = kCounterBytes;
+  c->window_bytes = align_up(window_bytes / 2 + (window_bytes & 1), 1024) * 2;
+  c->heap_bytes = align_up(heap_bytes, 1024);
+  c->total_bytes = c->flag_bytes + c->counter_bytes + c->window_bytes + c->heap_bytes;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, c->total_bytes);
+  if (e != cudaSuccess) { g_last_cuda_error = e; delete c; return EDM_ERR_CUDA; }
+  e = cudaMemset(p, 0, c->flag_bytes + c->counter_bytes);
+  if (e != cudaSuccess) { g_last_cuda_error = e; cudaFree(p); delete c; return EDM_ERR_CUDA; }
+  c->base[rank] = static_cast<char*>(p);
+  *out = c;
+  return EDM_OK;
+}
+
+int edm_comm_destroy(edm_comm_t* c) {
+  if (!c) return EDM_ERR_BAD_ARG;
+  cudaDeviceSynchronize();
+  for (int p = 0; p < c->world; ++p)
+    if (c->imported[p] && c->base[p]) cudaIpcCloseMemHandle(c->base[p]);
+  if (c->base[c->rank]) cudaFree(c->base[c->rank]);
+  delete c;
+  return EDM_OK;
+}
+
+int edm_comm_export(edm_comm_t* c, void* handle64) {
+  if (!c || !handle64) return EDM_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == EDM_IPC_HANDLE_BYTES, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  EDM_CUDA(cudaIpcGetMemHandle(&h, c->base[c->rank]));
+  std::memcpy(handle64, &h, sizeof(h));
+  return EDM_OK;
+}
+
+int edm_comm_import(edm_comm_t* c, int peer, const void* handle64) {
+  if (!c || !handle64 || peer < 0 || peer >= c->world || peer == c->rank) return EDM_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  EDM_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  c->base[peer] = static_cast<char*>(p);
+  c->imported[peer] = true;
+  return EDM_OK;
+}
+
+int edm_comm_link_local(edm_comm_t* c, int peer, edm_comm_t* other) {
+  if (!c || !other || peer < 0 || peer >= c->world || peer == c->rank) return EDM_ERR_BAD_ARG;
+  if (other->rank != peer || other->world != c->world || other->total_bytes != c->total_bytes)
+    return EDM_ERR_BAD_ARG;
+  c->base[peer] = other->base[other->rank];
+  c->imported[peer] = false;
+  return EDM_OK;
+}
+
+int edm_comm_heap_alloc(edm_comm_t* c, size_t bytes, void** out) {
+  if (!c || !out || bytes == 0) return EDM_ERR_BAD_ARG;
+  const size_t start = align_up(c->heap_used, 256);
+  if (start + bytes > c->heap_bytes) return EDM_ERR_CAPACITY;
+  *out = c->base[c->rank] + c->off_heap() + start;
+  c->heap_used = start + bytes;
+  return EDM_OK;
+}
+int edm_comm_heap_reset(edm_comm_t* c) {
+  if (!c) return EDM_ERR_BAD_ARG;
+  c->heap_used = 0;
+  return EDM_OK;
+}
+int edm_comm_rank(const edm_comm_t* c) { return c ? c->rank : -1; }
+int edm_comm_world(const edm_comm_t* c) { return c ? c->world : -1; }
+
+int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
+  if (!comm || !call) return EDM_ERR_BAD_ARG;
+  LaunchParams lp;
+  std::memset(&lp, 0, sizeof(lp));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = build_rank_params(comm, *call, lp.r[0], s);
+  if (rc) return rc;
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  const int grid = grid_for(lp.r[0], sms);
+  lp.num_vranks = 1;
+  lp.ctas_per_vrank = grid;
+  lp.timeout_ns = g_timeout_ns;
+  return launch_dtype(call->dtype, lp, grid, false, s);
+}
+
+int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls, int n, void* stream) {
+  if (!comms || !calls || n < 1 || n > kMaxVirtualRanks) return EDM_ERR_BAD_ARG;
+  LaunchParams lp;
+  std::memset(&lp, 0, sizeof(lp));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < n; ++i) {
+    if (!comms[i] || calls[i].dtype != calls[0].dtype) return EDM_ERR_BAD_ARG;
+    int rc = build_rank_params(comms[i], calls[i], lp.r[i], s);
+    if (rc) return rc;
+  }
+  const int sms = num_sms();
+  if (sms < n) return EDM_ERR_CUDA;
+  lp.num_vranks = n;
+  lp.ctas_per_vrank = sms / n;  // all CTAs co-resident: the emulated ranks wait on one another
+  lp.timeout_ns = g_timeout_ns;
+  return launch_dtype(calls[0].dtype, lp, lp.ctas_per_vrank * n, true, s);
+}
+
+static int tp_bf16(edm_comm_t* comm, int op, const void* a, int64_t lda, const void* b, int64_t ldb,
+                   void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, int32_t chunks, void* stream) {
+  edm_tp_call_t c;
+  std::memset(&c, 0, sizeof(c));
+  c.op = op; c.dtype = EDM_DTYPE_BF16;
+  c.a = a; c.lda = lda; c.b = b; c.ldb = ldb; c.d = d; c.ldd = ldd;
+  c.M = M; c.N = N; c.K = K; c.chunks = chunks;
+  return edm_tp_launch(comm, &c, stream);
+}
+int edm_gemm_rs_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b, int64_t ldb,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, void* stream) {
+  return tp_bf16(comm, EDM_OP_GEMM_RS, a, lda, b, ldb, d, ldd, M, N, K, 1, stream);
+}
+int edm_gemm_ar_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b, int64_t ldb,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, void* stream) {
+  return tp_bf16(comm, EDM_OP_GEMM_AR, a, lda, b, ldb, d, ldd, M, N, K, 1, stream);
+}
+int edm_ag_gemm_bf16(edm_comm_t* comm, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, int32_t chunks,
+                     void* stream) {
+  return tp_bf16(comm, EDM_OP_AG_GEMM, x, ldx, w, ldw, d, ldd, M, N, K, chunks, stream);
+}
+
+}  // extern "C"

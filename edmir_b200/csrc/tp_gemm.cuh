@@ -1,0 +1,645 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a with the tensor-parallel exchange
+// fused into it.  One kernel covers four modes:
+//
+//   PLAIN  D[M,N] = A[M,K] * B[N,K]^T
+//   RS     every rank computes a full partial; the rank that owns a block of rows receives the
+//          other ranks' partial tiles in its symmetric window and adds them in its epilogue
+//          (GEMM + reduce-scatter)
+//   AR     like RS with tile ownership dealt round-robin, then the owner stores the reduced tile
+//          into every rank's output (GEMM + all-reduce)
+//   AG     two helper warps per CTA push the local row shard of X to every peer while the
+//          tile loop consumes shards as their chunk flags arrive (all-gather + GEMM)
+//
+// Both operands are K-major (the reference's "TN" convention, EDM-IR/ir/c-extension/mma.cu:24-25).
+// Roles per CTA (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = peer
+// pushes (AG) / TMEM allocation, warps 4-7 = epilogue (TMEM -> registers -> smem -> global/peer).
+// Accumulators are double buffered in TMEM (2 x 256 columns) so the epilogue of tile i, which
+// is where the NVLink stores happen, overlaps the MMAs of tile i+1.
+//
+// Every wait (mbarrier or peer flag) is bounded: on expiry the kernel records a status code and
+// all remaining waits fall through, so the launch always terminates and frees its TMEM.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "ptx.cuh"
+
+namespace edm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockKBytes = 128;  // one 128B swizzle row of K per stage
+constexpr int kStages = 4;
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = 8;
+constexpr int kMaxVirtualRanks = 4;
+constexpr int kCommWarps = 2;
+constexpr int kTmemCols = 512;
+constexpr int kStageABytes = kBlockM * kBlockKBytes;  // 16 KiB
+constexpr int kStageBBytes = kBlockN * kBlockKBytes;  // 32 KiB
+constexpr int kStageBytes = kStageABytes + kStageBBytes;
+constexpr int kEpiRowBytes = 256;                      // staging row per pass
+constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;       // 8 KiB per epilogue warp
+constexpr int kSmemBytes = kStages * kStageBytes + 4 * kEpiWarpBytes + 1024 /*align*/ + 256;
+
+enum Mode : int32_t { kPlain = 0, kRS = 1, kAR = 2, kAG = 3 };
+
+// Status codes written to g_status[0]; g_status[1..7] carry details of the first failure.
+enum Status : uint32_t {
+  kOk = 0,
+  kTimeoutFullBar = 1,
+  kTimeoutEmptyBar = 2,
+  kTimeoutTmemFull = 3,
+  kTimeoutTmemEmpty = 4,
+  kTimeoutPartialFlag = 5,   // RS/AR: a peer's partial tile never arrived
+  kTimeoutResultFlag = 6,    // AR: an owner's reduced tile never arrived
+  kTimeoutGatherFlag = 7,    // AG: a peer's shard chunk never arrived
+};
+
+__device__ uint32_t g_status[16];
+
+struct alignas(64) RankParams {
+  CUtensorMap tmap_a[2];  // [0] main A (AG: local gather buffer); [1] 3xTF32 low part / AG local shard
+  CUtensorMap tmap_b[2];  // [0] main B; [1] 3xTF32 low part
+  int32_t M, N, K;        // GEMM extents on this rank (AG: M is the gathered row count)
+  int32_t rank, world;
+  int32_t mode;
+  int32_t passes;          // 1, or 3 for the split-fp32 path
+  uint32_t epoch;          // value a flag must reach in this call
+  int32_t max_owned;       // slots per source rank in a window
+  uint32_t partial_flag_off, result_flag_off, gather_flag_off;  // offsets in u32 into flags[]
+  int32_t ag_chunks;       // chunks per shard
+  int32_t ag_local_direct; // 1: own shard is read in place through tmap_a[1]
+  void* out;               // PLAIN/AG/AR: [M,N]; RS: [M/world,N]
+  int64_t ld_out;          // elements
+  const void* x_local;     // AG: this rank's shard [M/world,K]
+  int64_t ld_x;            // elements
+  uint32_t* counters;      // AG: local arrival counters [world*ag_chunks]
+  void* peer_out[kMaxRanks];   // AR: every rank's output as mapped here
+  char* win[kMaxRanks];        // every rank's window (parity half already selected)
+  uint32_t* flags[kMaxRanks];  // every rank's flag array
+  void* gather[kMaxRanks];     // AG: every rank's gather buffer [M,K]
+};
+
+struct LaunchParams {
+  int32_t num_vranks;     // 1 on real multi-GPU runs; >1 = ranks emulated inside one launch
+  int32_t ctas_per_vrank;
+  uint64_t timeout_ns;
+  RankParams r[kMaxVirtualRanks];
+};
+
+// ------------------------------------------------------------------ bounded waits
+__device__ __forceinline__ void report(uint32_t code, uint32_t a, uint32_t b, uint32_t c) {
+  if (atomicCAS(&g_status[0], 0u, code) == 0u) {
+    g_status[1] = blockIdx.x;
+    g_status[2] = threadIdx.x;
+    g_status[3] = a;
+    g_status[4] = b;
+    g_status[5] = c;
+    __threadfence();
+  }
+}
+__device__ __forceinline__ bool aborted() {
+  return *reinterpret_cast<volatile uint32_t*>(&g_status[0]) != 0u;
+}
+
+__device__ __noinline__ void wait_mbar_slow(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
+                                            uint32_t code, uint32_t info) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((spins++ & 15u) == 0u) {
+      if (aborted()) return;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) { report(code, info, parity, bar); return; }
+    }
+  }
+}
+__device__ __forceinline__ void wait_mbar(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
+                                          uint32_t code, uint32_t info) {
+  if (mbar_try_wait(bar, parity)) return;
+  wait_mbar_slow(bar, parity, timeout_ns, code, info);
+}
+
+// Wait until *flag (written by another GPU / CTA with release.sys) has reached `epoch`.
+__device__ __noinline__ void wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
+                                       uint32_t code, uint32_t info) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
+    if ((spins++ & 31u) == 0u) {
+      if (aborted()) return;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) { report(code, info, epoch, ld_relaxed_sys(flag)); return; }
+    }
+    __nanosleep(64);
+  }
+}
+
+// ------------------------------------------------------------------ tile enumeration
+struct Tile {
+  int m_blk, n_blk;
+  int owner;      // rank that ends up holding / reducing this tile
+  int owned_idx;  // index of the tile among the owner's tiles (slot / flag index)
+  int linear;     // m_blk * n_blocks + n_blk
+};
+
+// Walk an (mb x nb) grid in bands of 8 row-blocks so that concurrently running CTAs share
+// A and B panels in L2.
+__device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * nb;
+  const int band = i / per_band;
+  const int first = band * kBand;
+  const int rows = min(kBand, mb - first);
+  const int j = i - band * per_band;
+  m = first + j % rows;
+  n = j / rows;
+}
+
+struct TileWalk {
+  int mode, rank, world;
+  int m_blocks, n_blocks, total;
+  int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
+
+  __device__ TileWalk(const RankParams& p) {
+    mode = p.mode; rank = p.rank; world = p.world;
+    m_blocks = (p.M + kBlockM - 1) / kBlockM;
+    n_blocks = (p.N + kBlockN - 1) / kBlockN;
+    total = m_blocks * n_blocks;
+    const int rows_per_rank = p.M / max(world, 1);
+    mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % kBlockM == 0)
+                      ? rows_per_rank / kBlockM : 0;
+  }
+
+  __device__ Tile at(int i) const {
+    Tile t;
+    if (mode == kRS) {
+      // owners in the order rank+1, rank+2, ..., rank: peers' rows first, own rows last
+      const int per_owner = mb_per_rank * n_blocks;
+      const int d = i / per_owner;
+      t.owner = (rank + 1 + d) % world;
+      int lm, n;
+      band_order(i - d * per_owner, mb_per_rank, n_blocks, lm, n);
+      t.m_blk = t.owner * mb_per_rank + lm;
+      t.n_blk = n;
+      t.owned_idx = lm * n_blocks + n;
+    } else if (mode == kAR && world > 1) {
+      // tile `lin` belongs to rank lin % world; visit owners rank+1, ..., rank
+      int rem = i, o = rank, cnt = 0;
+      for (int d = 1; d <= world; ++d) {
+        o = (rank + d) % world;
+        cnt = (total - o + world - 1) / world;
+        if (rem < cnt) break;
+        rem -= cnt;
+      }
+      const int lin = rem * world + o;
+      t.owner = o;
+      t.owned_idx = rem;
+      t.m_blk = lin / n_blocks;
+      t.n_blk = lin % n_blocks;
+    } else if (mode == kAG && mb_per_rank > 0) {
+      int pm, n;
+      band_order(i, m_blocks, n_blocks, pm, n);
+      t.m_blk = (rank * mb_per_rank + pm) % m_blocks;  // own shard first, then rank+1, ...
+      t.n_blk = n;
+      t.owner = rank;
+      t.owned_idx = 0;
+    } else {
+      band_order(i, m_blocks, n_blocks, t.m_blk, t.n_blk);
+      t.owner = rank;
+      t.owned_idx = 0;
+    }
+    t.linear = t.m_blk * n_blocks + t.n_blk;
+    return t;
+  }
+};
+
+// ------------------------------------------------------------------ descriptors
+// K-major operand tile in shared memory, 128B rows, 128B swizzle, 8-row groups 1024B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;            // leading byte offset: unused with swizzled K-major
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;    // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version for sm_100
+  d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
+  return d;
+}
+template <bool kTf32>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  const uint32_t fmt = kTf32 ? 2u : 1u;  // 1 = BF16, 2 = TF32
+  return (1u << 4)                        // D format F32
+         | (fmt << 7) | (fmt << 10)       // A, B formats; both K-major (bits 15,16 = 0)
+         | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ output conversion
+template <typename OutT> struct OutPack;
+template <> struct OutPack<__nv_bfloat16> {
+  static constexpr int kColsPerPass = kEpiRowBytes / 2;  // 128
+  // 8 fp32 -> one 16B vector
+  __device__ static __forceinline__ uint4 pack8(const float* v) {
+    uint4 o;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+    return o;
+  }
+  __device__ static __forceinline__ void add16B(float* acc, uint4 w) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += __uint_as_float(u[i] << 16);
+      acc[2 * i + 1] += __uint_as_float(u[i] & 0xFFFF0000u);
+    }
+  }
+};
+template <> struct OutPack<float> {
+  static constexpr int kColsPerPass = kEpiRowBytes / 4;  // 64
+};
+
+// ------------------------------------------------------------------ the kernel
+template <bool kTf32, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
+  constexpr int kElemBytes = kTf32 ? 4 : 2;
+  constexpr int kBlockK = kBlockKBytes / kElemBytes;   // elements of K per stage
+  constexpr int kOutBytes = sizeof(OutT);
+  constexpr int kTileOutBytes = kBlockM * kBlockN * kOutBytes;
+  constexpr int kColsPerPass = kEpiRowBytes / kOutBytes;   // 128 (bf16) / 64 (fp32)
+  constexpr int kPasses = kBlockN / kColsPerPass;          // 2 / 4
+  constexpr int kChunksPerPass = kColsPerPass / 32;        // 4 / 2
+  constexpr int kVecPerRow = kEpiRowBytes / 16;            // 16
+  constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bars[2 * kStages + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int vr = blockIdx.x / lp.ctas_per_vrank;
+  const int cta = blockIdx.x - vr * lp.ctas_per_vrank;
+  const int num_ctas = lp.ctas_per_vrank;
+  const RankParams& P = lp.r[vr];
+  const uint64_t timeout_ns = lp.timeout_ns;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_epi = smem_base + kStages * kStageBytes;
+  const uint32_t bar_full = smem_u32(&bars[0]);
+  const uint32_t bar_empty = smem_u32(&bars[kStages]);
+  const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
+  const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 4);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
+
+  const TileWalk walk(P);
+  const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
+  const int num_kb = num_kb_pass * P.passes;
+  const int rows_per_rank = P.world > 0 ? P.M / P.world : P.M;
+
+  if (warp == 0) {
+    // ============================ TMA producer ============================
+    if (lane == 0) {
+      tma_prefetch_desc(&P.tmap_a[0]);
+      tma_prefetch_desc(&P.tmap_b[0]);
+      uint32_t it = 0;
+      for (int i = cta; i < walk.total; i += num_ctas) {
+        const Tile t = walk.at(i);
+        const int m0 = t.m_blk * kBlockM;
+        const int n0 = t.n_blk * kBlockN;
+        const CUtensorMap* amap = &P.tmap_a[0];
+        int a_row = m0;
+        if (P.mode == kAG) {
+          // wait for every shard chunk this row block touches
+          const int m1 = min(m0 + kBlockM, P.M);
+          const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
+          const int s_lo = m0 / rows_per_rank, s_hi = (m1 - 1) / rows_per_rank;
+          if (P.ag_local_direct && s_lo == P.rank) {
+            amap = &P.tmap_a[1];
+            a_row = m0 - P.rank * rows_per_rank;
+          } else {
+            for (int s = s_lo; s <= s_hi; ++s) {
+              const int lo = max(m0, s * rows_per_rank) - s * rows_per_rank;
+              const int hi = min(m1, (s + 1) * rows_per_rank) - s * rows_per_rank;
+              for (int c = lo / chunk_rows; c <= (hi - 1) / chunk_rows; ++c)
+                wait_flag(P.flags[P.rank] + P.gather_flag_off + s * P.ag_chunks + c, P.epoch,
+                          timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
+            }
+            fence_proxy_async_all();  // peer-written rows are read by the async proxy next
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          wait_mbar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
+          mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
+          // 3-pass split fp32: (hi,hi), (lo,hi), (hi,lo)
+          const int pass = kb / num_kb_pass;
+          const int kcol = (kb - pass * num_kb_pass) * kBlockK;
+          const CUtensorMap* am = (pass == 1) ? &P.tmap_a[1] : amap;
+          const CUtensorMap* bm = (pass == 2) ? &P.tmap_b[1] : &P.tmap_b[0];
+          const uint32_t sa = smem_base + s * kStageBytes;
+          tma_load_2d(sa, am, kcol, a_row, bar_full + 8 * s);
+          tma_load_2d(sa + kStageABytes, bm, kcol, n0, bar_full + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ============================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<kTf32>();
+      uint32_t it = 0, tile_iter = 0;
+      for (int i = cta; i < walk.total; i += num_ctas, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u;
+        wait_mbar(bar_tempty + 8 * acc, ((tile_iter >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty,
+                  tile_iter);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          wait_mbar(bar_full + 8 * s, (it / kStages) & 1u, timeout_ns, kTimeoutFullBar, it);
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * kStageBytes;
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + kStageABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockKBytes / 32; ++k) {
+            // each MMA consumes 32 bytes of K; descriptors advance in 16-byte units
+            umma_ss<kTf32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+        }
+        umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else if (warp < 2 + kCommWarps) {
+    // ============================ all-gather pushes ============================
+    if (P.mode == kAG && P.world > 1) {
+      const int cw = warp - 2;
+      const int gw = cta * kCommWarps + cw;
+      const int total_warps = num_ctas * kCommWarps;
+      const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
+      const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
+      const int first_d = P.ag_local_direct ? 1 : 0;
+      for (int c = 0; c < P.ag_chunks; ++c) {
+        const int r_lo = c * chunk_rows;
+        const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
+        const int64_t nvec = static_cast<int64_t>(max(r_hi - r_lo, 0)) * row_vecs;
+        for (int d = first_d; d < P.world; ++d) {
+          const int peer = (P.rank - d + P.world) % P.world;  // rank-1 needs this shard first
+          const char* src = static_cast<const char*>(P.x_local);
+          char* dst = static_cast<char*>(P.gather[peer]);
+          const int64_t src_ld = P.ld_x * kElemBytes;
+          const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
+          const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
+          constexpr int kUnroll = 4;
+          for (int64_t v0 = static_cast<int64_t>(gw) * 32 * kUnroll; v0 < nvec;
+               v0 += static_cast<int64_t>(total_warps) * 32 * kUnroll) {
+            uint4 buf[kUnroll];
+            int64_t row[kUnroll], col[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+              const int64_t v = v0 + u * 32 + lane;
+              row[u] = v / row_vecs;
+              col[u] = v - row[u] * row_vecs;
+              if (v < nvec) buf[u] = ld_cg_v4(src + (r_lo + row[u]) * src_ld + col[u] * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+              const int64_t v = v0 + u * 32 + lane;
+              if (v < nvec) st_global_v4(dst + (dst_row0 + r_lo + row[u]) * dst_ld + col[u] * 16, buf[u]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) {
+            // last arriving warp of this GPU publishes the chunk to the peer
+            fence_acq_rel_sys();
+            uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
+            const uint32_t prev = atomicAdd(ctr, 1u);
+            if (prev == static_cast<uint32_t>(total_warps - 1)) {
+              *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;
+              fence_acq_rel_sys();
+              st_release_sys(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, P.epoch);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ============================ epilogue ============================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t stage_smem = smem_epi + q * kEpiWarpBytes;
+    const int row = q * 32 + lane;  // row within the tile owned by this thread
+    uint32_t tile_iter = 0;
+    const bool fused = (P.mode == kRS || P.mode == kAR) && P.world > 1;
+    for (int i = cta; i < walk.total; i += num_ctas, ++tile_iter) {
+      const Tile t = walk.at(i);
+      const uint32_t acc = tile_iter & 1u;
+      const bool mine = (t.owner == P.rank);
+      const bool reduce = fused && mine;
+      const bool push_partial = fused && !mine;
+
+      if (reduce) {
+        // partial tiles (this warp's quarter) from every other rank must have landed
+        if (lane < P.world && lane != P.rank)
+          wait_flag(P.flags[P.rank] + P.partial_flag_off +
+                        (static_cast<uint32_t>(lane) * P.max_owned + t.owned_idx) * 4 + q,
+                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | t.owned_idx);
+        __syncwarp();
+      }
+      if (lane == 0)
+        wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter);
+      __syncwarp();
+      tc_fence_after();
+
+      // destinations of this tile
+      const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
+      const int valid_cols = min(kBlockN, P.N - n0);
+      int valid_rows = min(kBlockM, P.M - m0);
+      int ndst = 1;
+      char* dst_base[kMaxRanks];
+      int64_t dst_ld;  // bytes
+      if (push_partial) {
+        dst_base[0] = P.win[t.owner] +
+                      (static_cast<int64_t>(P.rank) * P.max_owned + t.owned_idx) * kTileOutBytes;
+        dst_ld = kBlockN * kOutBytes;
+        valid_rows = kBlockM;
+      } else if (P.mode == kRS) {
+        const int lm0 = m0 - P.rank * rows_per_rank;
+        dst_base[0] = static_cast<char*>(P.out) + (static_cast<int64_t>(lm0) * P.ld_out + n0) * kOutBytes;
+        dst_ld = P.ld_out * kOutBytes;
+      } else if (P.mode == kAR && fused) {
+        ndst = P.world;
+        for (int d = 0; d < P.world; ++d) {
+          const int peer = (P.rank + d) % P.world;  // own copy first
+          dst_base[d] = static_cast<char*>(P.peer_out[peer]) +
+                        (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
+        }
+        dst_ld = P.ld_out * kOutBytes;
+      } else {
+        dst_base[0] = static_cast<char*>(P.out) + (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
+        dst_ld = P.ld_out * kOutBytes;
+      }
+      const int push_cols = push_partial ? kBlockN : valid_cols;
+
+      const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int h = 0; h < kPasses; ++h) {
+#pragma unroll
+        for (int j = 0; j < kChunksPerPass; ++j) {
+          const int c = h * kChunksPerPass + j;  // 32-column chunk of the tile
+          uint32_t raw[32];
+          tmem_ld_32x32(taddr + c * 32, raw);
+          tmem_ld_wait();
+          if (c == kBlockN / 32 - 1) {
+            // accumulator fully read: hand the TMEM buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          }
+          float v[32];
+          if (reduce) {
+            // fixed summation order over ranks keeps the result run-to-run deterministic
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0.f;
+            for (int src = 0; src < P.world; ++src) {
+              if (src == P.rank) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] += __uint_as_float(raw[e]);
+              } else {
+                const char* slot = P.win[P.rank] +
+                                   (static_cast<int64_t>(src) * P.max_owned + t.owned_idx) * kTileOutBytes +
+                                   static_cast<int64_t>(row) * (kBlockN * kOutBytes) + c * 32 * kOutBytes;
+#pragma unroll
+                for (int w = 0; w < 32 / kOutPerVec; ++w) {
+                  const uint4 x = ld_cg_v4(slot + w * 16);
+                  if constexpr (kOutBytes == 2) {
+                    OutPack<__nv_bfloat16>::add16B(&v[w * 8], x);
+                  } else {
+                    v[w * 4 + 0] += __uint_as_float(x.x);
+                    v[w * 4 + 1] += __uint_as_float(x.y);
+                    v[w * 4 + 2] += __uint_as_float(x.z);
+                    v[w * 4 + 3] += __uint_as_float(x.w);
+                  }
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+          }
+          // registers -> staging: thread owns row `lane`; 16B vectors XOR-swizzled by row
+#pragma unroll
+          for (int w = 0; w < 32 / kOutPerVec; ++w) {
+            uint4 o;
+            if constexpr (kOutBytes == 2) {
+              o = OutPack<__nv_bfloat16>::pack8(&v[w * 8]);
+            } else {
+              o.x = __float_as_uint(v[w * 4 + 0]); o.y = __float_as_uint(v[w * 4 + 1]);
+              o.z = __float_as_uint(v[w * 4 + 2]); o.w = __float_as_uint(v[w * 4 + 3]);
+            }
+            const int lv = j * (32 / kOutPerVec) + w;  // logical 16B vector within the staged row
+            st_shared_v4(stage_smem + lane * kEpiRowBytes + ((lv ^ (lane & 7)) << 4), o);
+          }
+        }
+        __syncwarp();
+        // staging -> global: two full 256B rows per warp instruction
+        const int col0 = h * kColsPerPass;  // first tile column of this pass
+        for (int d = 0; d < ndst; ++d) {
+#pragma unroll 4
+          for (int itr = 0; itr < 16; ++itr) {
+            const int lr = itr * 2 + (lane >> 4);  // row within the warp's 32 rows
+            const int lv = lane & 15;
+            const uint4 x = ld_shared_v4(stage_smem + lr * kEpiRowBytes + ((lv ^ (lr & 7)) << 4));
+            const int col = col0 + lv * kOutPerVec;
+            if (q * 32 + lr < valid_rows && col < push_cols)
+              st_global_v4(dst_base[d] + static_cast<int64_t>(q * 32 + lr) * dst_ld + col * kOutBytes, x);
+          }
+        }
+        __syncwarp();
+      }
+
+      if (push_partial) {
+        __syncwarp();
+        if (lane == 0) {
+          fence_acq_rel_sys();
+          st_release_sys(P.flags[t.owner] + P.partial_flag_off +
+                             (static_cast<uint32_t>(P.rank) * P.max_owned + t.owned_idx) * 4 + q,
+                         P.epoch);
+        }
+      } else if (P.mode == kAR && fused) {
+        __syncwarp();
+        if (lane < P.world && lane != P.rank) {
+          fence_acq_rel_sys();
+          st_release_sys(P.flags[lane] + P.result_flag_off + static_cast<uint32_t>(t.linear) * 4 + q,
+                         P.epoch);
+        }
+      }
+    }
+
+    if (P.mode == kAR && fused) {
+      // the call is complete on this rank only when every other owner's tiles have arrived
+      const int gw = cta * 4 + q;
+      const int total_warps = num_ctas * 4;
+      for (int base = gw * 32; base < walk.total * 4; base += total_warps * 32) {
+        const int idx = base + lane;  // (tile, quarter) pair
+        if (idx < walk.total * 4 && (idx >> 2) % P.world != P.rank)
+          wait_flag(P.flags[P.rank] + P.result_flag_off + idx, P.epoch, timeout_ns,
+                    kTimeoutResultFlag, idx);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (aborted()) __nanosleep(200000);  // let loads that are still in flight land before smem goes away
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Split fp32 into a tf32-representable high part and the (tf32-rounded) remainder.
+__global__ void split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                  float* __restrict__ lo, int64_t rows, int64_t cols, int64_t ld) {
+  const int64_t n = rows * cols;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float v = x[r * ld + c];
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+    const float rem = v - __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rem));
+    hi[i] = __uint_as_float(h);
+    lo[i] = __uint_as_float(l);
+  }
+}
+
+}  // namespace edm

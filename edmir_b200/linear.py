@@ -1,0 +1,119 @@
+"""Single-GPU GEMM operators on torch tensors, backed by the sm_100a kernel.
+
+Operand convention is the reference's (EDM-IR/ir/c-extension/mma.cu:24-25): ``a`` is
+``[M, K]``, ``b`` is ``[N, K]`` (both K-major), the result is ``[M, N]``.  A torch
+``nn.Linear`` weight is already ``[N, K]``; a ``[K, N]`` weight is prepared once with
+``prepare_weight``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("operands must be CUDA tensors (there is no CPU path)")
+
+
+def _check_2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must have unit stride along its last dimension")
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def prepare_weight(w_kn: torch.Tensor) -> torch.Tensor:
+    """``[K, N]`` weight -> K-major ``[N, K]`` copy (done once, outside the hot path)."""
+    return w_kn.t().contiguous()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ b[N,K]^T`` in bf16 with fp32 accumulation."""
+    _require_cuda(a, b)
+    _check_2d(a, "a")
+    _check_2d(b, "b")
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise ValueError("gemm expects bfloat16 operands")
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    else:
+        _check_2d(out, "out")
+        if tuple(out.shape) != (M, N) or out.dtype != torch.bfloat16:
+            raise ValueError("out must be bfloat16 of shape [M, N]")
+    lib = _lib.load()
+    rc = lib.edm_gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),
+                           out.stride(0), M, N, K, _stream())
+    _lib.check(rc, "edm_gemm_bf16")
+    return out
+
+
+def gemm_fp32_workspace_bytes(M: int, N: int, K: int) -> int:
+    return int(_lib.load().edm_gemm_fp32_workspace_bytes(M, N, K))
+
+
+def gemm_fp32(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
+              workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = a @ b^T`` for fp32 tensors at fp32-level accuracy (three tf32 tensor-core
+    passes over a high/low split of each operand)."""
+    _require_cuda(a, b)
+    _check_2d(a, "a")
+    _check_2d(b, "b")
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise ValueError("gemm_fp32 expects float32 operands")
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    need = gemm_fp32_workspace_bytes(M, N, K)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    lib = _lib.load()
+    rc = lib.edm_gemm_fp32(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),
+                           out.stride(0), M, N, K, workspace.data_ptr(),
+                           workspace.numel() * workspace.element_size(), _stream())
+    _lib.check(rc, "edm_gemm_fp32")
+    return out
+
+
+def tiled_mma_bf16_bf16_bf16_fp32(a: torch.Tensor, b: torch.Tensor,
+                                  c: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in for the reference's only native operator (EDM-IR/ir/c-extension/mma.cu:175,
+    :267-271): ``bf16(a[M,K] @ b[N,K]^T (+ c))`` with fp32 accumulation, for any M, N, K
+    rather than the single 32x32x16 tile.  Shape or dtype mismatches raise ``ValueError``
+    instead of terminating the process (mma.cu:119-136)."""
+    if c is None:
+        return gemm(a, b)
+    if c.dtype != torch.float32 or tuple(c.shape) != (a.shape[0], b.shape[0]):
+        raise ValueError("c must be float32 of shape [M, N]")
+    acc = gemm_fp32(a.float(), b.float())
+    return (acc + c).to(torch.bfloat16)
+
+
+def status() -> list[int]:
+    """Device status words (all zero unless a bounded device-side wait expired)."""
+    buf = (C.c_uint32 * 16)()
+    _lib.check(_lib.load().edm_status_read(buf), "edm_status_read")
+    return list(buf)
+
+
+def clear_status() -> None:
+    _lib.check(_lib.load().edm_status_clear(), "edm_status_clear")
+
+
+def set_timeout_ms(ms: int) -> None:
+    _lib.check(_lib.load().edm_set_timeout_ms(int(ms)), "edm_set_timeout_ms")

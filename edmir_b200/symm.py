@@ -1,0 +1,182 @@
+"""Symmetric memory contexts and the fused tensor-parallel linear operators.
+
+One ``SymmetricContext`` per rank owns a device allocation with the same layout on every rank
+(flag words, a double-buffered window for tiles / shards in flight, a bump heap for tensors
+peers store into).  Peers map each other's allocation through CUDA IPC; the handles travel
+over ``torch.distributed`` (any backend), which is used for bootstrap only -- the data path is
+in-kernel stores over NVLink.
+
+``EmulatedGroup`` builds W contexts on ONE device and runs the W ranks' kernels as a single
+cooperative launch, each rank on 1/W of the SMs.  That is how the multi-rank protocol is
+checked on a single GPU (kernels that wait on each other may not be separate launches there).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import torch
+
+from . import _lib
+from .linear import _check_2d, _require_cuda, _stream
+
+_OPS = {"gemm_rs": _lib.EDM_OP_GEMM_RS, "gemm_ar": _lib.EDM_OP_GEMM_AR, "ag_gemm": _lib.EDM_OP_AG_GEMM}
+_DTYPES = {torch.bfloat16: _lib.EDM_DTYPE_BF16, torch.float32: _lib.EDM_DTYPE_FP32}
+
+
+class _DevicePtr:
+    """Exposes a raw device range through ``__cuda_array_interface__`` (as bytes)."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self._owner = owner  # keeps the context alive while views exist
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
+
+
+def default_window_bytes(max_m: int, max_n: int, max_k: int, world: int) -> int:
+    """Window size (both parities) that fits GEMM+RS/AR of [max_m, max_n] and AG of [max_m, max_k]."""
+    tiles = -(-max_m // 128) * -(-max_n // 256)
+    slots = (-(-tiles // world) + 1) * world * 128 * 256 * 4
+    gather = max_m * max_k * 2
+    return 2 * max(slots, gather)
+
+
+class SymmetricContext:
+    def __init__(self, rank: int, world: int, window_bytes: int, heap_bytes: int, device=None):
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self.rank, self.world = rank, world
+        self._lib = _lib.load()
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.edm_comm_create(rank, world, window_bytes, heap_bytes, C.byref(handle)),
+                       "edm_comm_create")
+        self._h = handle
+        self._workspace: torch.Tensor | None = None
+
+    # ---------------------------------------------------------------- setup
+    @classmethod
+    def create(cls, window_bytes: int, heap_bytes: int, group=None) -> "SymmetricContext":
+        """Collective over ``group``: allocate, exchange IPC handles, map every peer."""
+        import torch.distributed as dist
+
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        ctx = cls(rank, world, window_bytes, heap_bytes)
+        if world > 1:
+            buf = C.create_string_buffer(_lib.EDM_IPC_HANDLE_BYTES)
+            _lib.check(ctx._lib.edm_comm_export(ctx._h, buf), "edm_comm_export")
+            handles: list = [None] * world
+            dist.all_gather_object(handles, bytes(buf.raw), group=group)
+            for peer, raw in enumerate(handles):
+                if peer == rank:
+                    continue
+                _lib.check(ctx._lib.edm_comm_import(ctx._h, peer, C.create_string_buffer(raw, len(raw))),
+                           "edm_comm_import")
+            dist.barrier(group=group)
+        return ctx
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            self._lib.edm_comm_destroy(self._h)
+            self._h = None
+
+    # ---------------------------------------------------------------- symmetric tensors
+    def empty(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Tensor in the symmetric heap (peers can store into it).  Every rank must allocate
+        the same sequence of shapes."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        ptr = C.c_void_p()
+        _lib.check(self._lib.edm_comm_heap_alloc(self._h, max(nbytes, 1), C.byref(ptr)), "edm_comm_heap_alloc")
+        raw = torch.as_tensor(_DevicePtr(ptr.value, max(nbytes, 1), self), device=self.device)
+        return raw[:nbytes].view(dtype).view(*shape)
+
+    def reset_heap(self) -> None:
+        _lib.check(self._lib.edm_comm_heap_reset(self._h), "edm_comm_heap_reset")
+
+    # ---------------------------------------------------------------- launches
+    def _call(self, op: str, a, b, out, chunks: int = 1) -> "_lib.TpCall":
+        _require_cuda(a, b, out)
+        for t, n in ((a, "a"), (b, "b"), (out, "out")):
+            _check_2d(t, n)
+        if a.dtype != b.dtype or a.dtype != out.dtype or a.dtype not in _DTYPES:
+            raise ValueError("operands and output must share a dtype of bfloat16 or float32")
+        N, K = b.shape
+        if a.shape[1] != K:
+            raise ValueError("inner dimensions differ")
+        M = a.shape[0] * self.world if op == "ag_gemm" else a.shape[0]
+        want = (M // self.world, N) if op == "gemm_rs" else (M, N)
+        if tuple(out.shape) != want:
+            raise ValueError(f"out must have shape {want} for {op}, got {tuple(out.shape)}")
+        call = _lib.TpCall()
+        call.op, call.dtype = _OPS[op], _DTYPES[a.dtype]
+        call.a, call.lda = a.data_ptr(), a.stride(0)
+        call.b, call.ldb = b.data_ptr(), b.stride(0)
+        call.d, call.ldd = out.data_ptr(), out.stride(0)
+        call.M, call.N, call.K = M, N, K
+        call.chunks = chunks
+        if a.dtype == torch.float32:
+            need = int(self._lib.edm_gemm_fp32_workspace_bytes(a.shape[0], N, K))
+            if self._workspace is None or self._workspace.numel() < need:
+                self._workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+            call.workspace, call.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
+        return call
+
+    def _launch(self, op: str, a, b, out, chunks: int = 1):
+        call = self._call(op, a, b, out, chunks)
+        _lib.check(self._lib.edm_tp_launch(self._h, C.byref(call), _stream()), f"edm_tp_launch({op})")
+        return out
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel linear + reduce-scatter: ``out[M/W, N]`` = rows ``rank*M/W ..`` of
+        ``sum_r a_r @ b_r^T``."""
+        if out is None:
+            out = torch.empty((a.shape[0] // self.world, b.shape[0]), dtype=a.dtype, device=a.device)
+        return self._launch("gemm_rs", a, b, out)
+
+    def gemm_ar(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel linear + all-reduce: every rank ends with ``sum_r a_r @ b_r^T``.  ``out``
+        must come from ``self.empty`` (peers store reduced tiles straight into it)."""
+        if out is None:
+            out = self.empty((a.shape[0], b.shape[0]), a.dtype)
+        return self._launch("gemm_ar", a, b, out)
+
+    def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                chunks: int = 1) -> torch.Tensor:
+        """All-gather of the token-sharded ``x[M/W, K]`` fused with ``out[M, N/W] = X @ w^T``."""
+        if out is None:
+            out = torch.empty((x.shape[0] * self.world, w.shape[0]), dtype=x.dtype, device=x.device)
+        return self._launch("ag_gemm", x, w, out, chunks)
+
+
+class EmulatedGroup:
+    """W ranks on one device; ``run`` executes all of them in one cooperative launch."""
+
+    def __init__(self, world: int, window_bytes: int, heap_bytes: int, device=None):
+        if not 1 <= world <= 4:
+            raise ValueError("an emulated group holds 1 to 4 ranks")
+        self.world = world
+        self.ranks = [SymmetricContext(r, world, window_bytes, heap_bytes, device) for r in range(world)]
+        lib = self.ranks[0]._lib
+        for a in self.ranks:
+            for b in self.ranks:
+                if a is not b:
+                    _lib.check(lib.edm_comm_link_local(a._h, b.rank, b._h), "edm_comm_link_local")
+
+    def run(self, op: str, a_list, b_list, out_list, chunks: int = 1):
+        calls = (_lib.TpCall * self.world)()
+        for r, ctx in enumerate(self.ranks):
+            calls[r] = ctx._call(op, a_list[r], b_list[r], out_list[r], chunks)
+        handles = (C.c_void_p * self.world)(*[ctx._h for ctx in self.ranks])
+        lib = self.ranks[0]._lib
+        _lib.check(lib.edm_tp_launch_emulated(handles, calls, self.world, _stream()),
+                   f"edm_tp_launch_emulated({op})")
+        return out_list
+
+    def close(self) -> None:
+        for ctx in self.ranks:
+            ctx.close()

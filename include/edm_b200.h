@@ -1,0 +1,165 @@
+/* C ABI of the B200 backend for EDM-IR's tensor-parallel linear layer.
+ *
+ * Everything is plain C: raw device pointers, sizes in elements, a CUDA stream passed as
+ * void*, integer status returns.  Nothing here allocates on the launch path; the caller owns
+ * every tensor, the library owns only what edm_comm_create() hands out.
+ *
+ * Operand convention (all GEMM entry points): A is [M,K] row-major, B is [N,K] row-major
+ * (both K-major, "TN"), D is [M,N] row-major.  This is the convention of the reference's only
+ * GEMM operator, tiled_mma_bf16_bf16_bf16_fp32 (EDM-IR/ir/c-extension/mma.cu:24-25, :175).
+ * Leading dimensions are in elements and must make every row start 16-byte aligned.
+ *
+ * The reference has no collective, window or selector code; where an entry point has no
+ * reference counterpart its comment says which reference concept it serves instead.
+ */
+#ifndef EDM_B200_H_
+#define EDM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define EDM_OK 0
+#define EDM_ERR_BAD_ARG 1        /* shape / alignment / null pointer */
+#define EDM_ERR_CUDA 2           /* a CUDA call failed; see edm_last_cuda_error() */
+#define EDM_ERR_DEVICE_TIMEOUT 3 /* a bounded device-side wait expired; see edm_status_read() */
+#define EDM_ERR_CAPACITY 4       /* window / flag / heap space too small for this shape */
+#define EDM_ERR_NOT_SYMMETRIC 5  /* all-reduce output does not live in the symmetric heap */
+#define EDM_ERR_UNSUPPORTED 6
+
+#define EDM_DTYPE_BF16 0 /* bf16 in, fp32 accumulate, bf16 out */
+#define EDM_DTYPE_FP32 1 /* fp32 in/out through three tf32 tensor-core passes (hi*hi+lo*hi+hi*lo) */
+
+#define EDM_OP_GEMM 0    /* D = A * B^T */
+#define EDM_OP_GEMM_RS 1 /* row-parallel linear + reduce-scatter: rank r gets rows r*M/W.. of sum_r A_r B_r^T */
+#define EDM_OP_GEMM_AR 2 /* row-parallel linear + all-reduce: every rank gets sum_r A_r B_r^T */
+#define EDM_OP_AG_GEMM 3 /* all-gather of token-sharded X, then D_r = X * W_r^T */
+
+#define EDM_MAX_RANKS 8
+#define EDM_IPC_HANDLE_BYTES 64
+
+/* Library/ABI version, and the last cudaError_t seen by any entry point on this thread's device
+ * (replaces the reference wrapper's throw of std::runtime_error, mma.cu:248-252). */
+int edm_version(void);
+int edm_last_cuda_error(void);
+
+/* Device-side status words of the current device: out[0] = 0 or a timeout code, out[1..7] =
+ * CTA, thread and wait details of the first failure.  Synchronises the device.
+ * edm_status_clear() re-arms it.  (The reference exits the process on errors,
+ * mma.cu:119-136; here errors are returned, never fatal.) */
+int edm_status_read(uint32_t out[16]);
+int edm_status_clear(void);
+
+/* Upper bound for every device-side wait, in milliseconds (default 2000). */
+int edm_set_timeout_ms(uint32_t ms);
+
+/* ---- single-GPU GEMM ---------------------------------------------------------------
+ * Replaces run_tiled_mma / tiled_mma_bf16_bf16_bf16_fp32 (EDM-IR/ir/c-extension/mma.cu:168-271)
+ * for arbitrary M, N, K.  Asynchronous on `stream`. */
+int edm_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+                  int64_t M, int64_t N, int64_t K, void* stream);
+
+/* fp32 GEMM with fp32-level accuracy on the tensor cores.  `workspace` holds the tf32 high/low
+ * splits of A and B and must be at least edm_gemm_fp32_workspace_bytes(M,N,K) bytes. */
+size_t edm_gemm_fp32_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int edm_gemm_fp32(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+                  int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* ---- symmetric memory and peer windows ---------------------------------------------
+ * No reference counterpart: the reference only names collectives as op strings
+ * (EDM-IR/ir/ops.py:32-35) and records `backend` as free text (EDM-IR/ir/uop.py:49).
+ * One context per rank.  It owns a single device allocation, laid out identically on every rank:
+ * flag words, a double-buffered window for in-flight tiles / gathered shards, and a bump heap
+ * for tensors that peers write directly (all-reduce outputs). */
+typedef struct edm_comm edm_comm_t;
+
+int edm_comm_create(int rank, int world, size_t window_bytes, size_t heap_bytes, edm_comm_t** out);
+int edm_comm_destroy(edm_comm_t* comm);
+/* Exchange: export this rank's allocation as a 64-byte IPC handle; import every peer's. */
+int edm_comm_export(edm_comm_t* comm, void* handle64);
+int edm_comm_import(edm_comm_t* comm, int peer, const void* handle64);
+/* Same-process peers (several contexts on one GPU, or on GPUs with peer access enabled). */
+int edm_comm_link_local(edm_comm_t* comm, int peer, edm_comm_t* peer_comm);
+/* Bump allocation from the symmetric heap; every rank must make the same sequence of calls. */
+int edm_comm_heap_alloc(edm_comm_t* comm, size_t bytes, void** out);
+int edm_comm_heap_reset(edm_comm_t* comm);
+int edm_comm_rank(const edm_comm_t* comm);
+int edm_comm_world(const edm_comm_t* comm);
+
+/* ---- fused tensor-parallel linear ----------------------------------------------------
+ * These are the launches a lowering of compute.gemm + comm.reduce_scatter / comm.all_reduce /
+ * comm.all_gather node pairs (EDM-IR/ir/ops.py:29,32-34) turns into.  Every rank of the
+ * context calls the same entry point with the same shape, in the same order. */
+typedef struct {
+  int32_t op;    /* EDM_OP_* */
+  int32_t dtype; /* EDM_DTYPE_* */
+  const void* a; /* GEMM_RS / GEMM_AR: A_r [M, K]; AG_GEMM: X_r [M/world, K] */
+  int64_t lda;
+  const void* b; /* B_r [N, K] */
+  int64_t ldb;
+  void* d; /* GEMM_RS: [M/world, N]; GEMM_AR: [M, N] in the symmetric heap; AG_GEMM: [M, N] */
+  int64_t ldd;
+  int64_t M, N, K; /* per-rank GEMM extents; for AG_GEMM M counts the gathered rows */
+  int32_t chunks;  /* AG_GEMM: chunks per shard (>= 1); ignored otherwise */
+  int32_t reserved;
+  void* workspace; /* EDM_DTYPE_FP32 only: tf32 split scratch */
+  size_t workspace_bytes;
+} edm_tp_call_t;
+
+int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream);
+
+/* Runs n ranks' calls as ONE cooperative launch on the current device (rank i uses 1/n of the
+ * SMs).  This is how the multi-rank protocol is exercised on a single GPU: kernels that wait on
+ * one another must not be separate launches on one device. */
+int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls, int n, void* stream);
+
+/* Convenience wrappers over edm_tp_launch for the bf16 layer ops. */
+int edm_gemm_rs_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b, int64_t ldb,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, void* stream);
+int edm_gemm_ar_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b, int64_t ldb,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, void* stream);
+int edm_ag_gemm_bf16(edm_comm_t* comm, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                     void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, int32_t chunks,
+                     void* stream);
+
+/* ---- schedule selector -----------------------------------------------------------------
+ * Integer restatement of the reference's cost evaluation: a chunked GEMM->collective pipeline
+ * is scored exactly as analyze_critical_path (EDM-IR/ir/analysis.py:36-65) scores the graph
+ * EDMBuilder (EDM-IR/ir/builder.py:22-110) builds for it, with the alpha-beta communication
+ * term of paper/mlsys-2027/model.md:98 and the split overheads of model.md:161-168.
+ * All durations are integers (nanoseconds or any other unit) so the result is bit-exact. */
+typedef struct {
+  int64_t gemm_total;      /* duration of the unchunked GEMM */
+  int64_t comm_bytes;      /* bytes the unchunked collective moves per GPU */
+  int64_t alpha;           /* fixed cost per collective launch / chunk */
+  int64_t beta_num;        /* transfer cost = ceil(bytes * beta_num / beta_den) */
+  int64_t beta_den;
+  int64_t split_overhead;  /* added to every GEMM chunk when chunks > 1 */
+  int32_t comm_first;      /* 0: GEMM chunk feeds collective chunk (RS/AR); 1: collective feeds GEMM (AG) */
+  int32_t reserved;
+} edm_cost_params_t;
+
+typedef struct {
+  int64_t makespan;        /* critical-path duration of the candidate */
+  int64_t exposed_comm;    /* summed duration of comm nodes on the critical path */
+  int64_t total_comm;
+  int64_t gemm_chunk;      /* duration of one GEMM chunk */
+  int64_t comm_chunk;      /* duration of one collective chunk */
+} edm_candidate_cost_t;
+
+/* Score one candidate. */
+int edm_schedule_cost(const edm_cost_params_t* p, int32_t chunks, edm_candidate_cost_t* out);
+/* Score candidates[0..n) and return the index of the smallest makespan (ties: lowest index) in
+ * *chosen; costs may be NULL. */
+int edm_select_schedule(const edm_cost_params_t* p, const int32_t* candidates, int32_t n,
+                        edm_candidate_cost_t* costs, int32_t* chosen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EDM_B200_H_ */
