@@ -100,8 +100,14 @@ int launch_dtype(int dtype, const LaunchParams& lp, int grid, bool coop, cudaStr
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Split-fp32 scratch: tf32 high/low copies of A and B, then one fp32 running-sum tile per CTA.
+constexpr int kSegKBlocks = 8;      // 256 K elements per TMEM accumulation segment
+constexpr int kMaxGridCtas = 256;   // upper bound on CTAs of one launch
+constexpr size_t kRunningSumBytes = static_cast<size_t>(kMaxGridCtas) * kBlockM * kBlockN * 4;
+
 size_t split_ws_bytes(int64_t M, int64_t N, int64_t K) {
-  return 2 * (align_up(static_cast<size_t>(M) * K * 4, 256) + align_up(static_cast<size_t>(N) * K * 4, 256));
+  return 2 * (align_up(static_cast<size_t>(M) * K * 4, 256) + align_up(static_cast<size_t>(N) * K * 4, 256)) +
+         kRunningSumBytes;
 }
 
 // Fills tmap_a/tmap_b (and runs the tf32 split for fp32) for a GEMM A[M,K] x B[N,K].
@@ -139,6 +145,8 @@ int prepare_operands(RankParams& P, int dtype, const void* a, int64_t lda, int64
   if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN))) return rc;
   if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN))) return rc;
   P.passes = 3;
+  P.seg_kblocks = kSegKBlocks;
+  P.scratch = reinterpret_cast<float*>(w + 2 * a_sz + 2 * b_sz);
   return EDM_OK;
 }
 

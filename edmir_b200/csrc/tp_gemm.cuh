@@ -75,6 +75,9 @@ struct alignas(64) RankParams {
   const void* x_local;     // AG: this rank's shard [M/world,K]
   int64_t ld_x;            // elements
   uint32_t* counters;      // AG: local arrival counters [world*ag_chunks]
+  float* scratch;          // split-fp32: running fp32 sums, one kBlockM x kBlockN tile per CTA
+  int32_t seg_kblocks;     // split-fp32: K blocks accumulated in TMEM before folding into scratch (0 = all)
+  int32_t pad0;
   void* peer_out[kMaxRanks];   // AR: every rank's output as mapped here
   char* win[kMaxRanks];        // every rank's window (parity half already selected)
   uint32_t* flags[kMaxRanks];  // every rank's flag array
@@ -320,7 +323,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 
   const TileWalk walk(P);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
-  const int num_kb = num_kb_pass * P.passes;
+  // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
+  // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
+  // folds each segment into a running sum kept with ordinary fp32 adds.
+  const int seg_kb = (P.seg_kblocks > 0 && P.seg_kblocks < num_kb_pass) ? P.seg_kblocks : num_kb_pass;
+  const int num_segs = (num_kb_pass + seg_kb - 1) / seg_kb;
   const int rows_per_rank = P.world > 0 ? P.M / P.world : P.M;
 
   if (warp == 0) {
@@ -354,18 +361,21 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             fence_proxy_async_all();  // peer-written rows are read by the async proxy next
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % kStages;
-          wait_mbar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
-          mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
-          // 3-pass split fp32: (hi,hi), (lo,hi), (hi,lo)
-          const int pass = kb / num_kb_pass;
-          const int kcol = (kb - pass * num_kb_pass) * kBlockK;
-          const CUtensorMap* am = (pass == 1) ? &P.tmap_a[1] : amap;
-          const CUtensorMap* bm = (pass == 2) ? &P.tmap_b[1] : &P.tmap_b[0];
-          const uint32_t sa = smem_base + s * kStageBytes;
-          tma_load_2d(sa, am, kcol, a_row, bar_full + 8 * s);
-          tma_load_2d(sa + kStageABytes, bm, kcol, n0, bar_full + 8 * s);
+        for (int seg = 0; seg < num_segs; ++seg) {
+          const int j0 = seg * seg_kb, j1 = min(j0 + seg_kb, num_kb_pass);
+          for (int pass = 0; pass < P.passes; ++pass) {
+            // split fp32: (lo,hi), (hi,lo), then (hi,hi) so the small terms meet a small accumulator
+            const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
+            const CUtensorMap* bm = (P.passes == 3 && pass == 1) ? &P.tmap_b[1] : &P.tmap_b[0];
+            for (int j = j0; j < j1; ++j, ++it) {
+              const uint32_t s = it % kStages;
+              wait_mbar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
+              mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
+              const uint32_t sa = smem_base + s * kStageBytes;
+              tma_load_2d(sa, am, j * kBlockK, a_row, bar_full + 8 * s);
+              tma_load_2d(sa + kStageABytes, bm, j * kBlockK, n0, bar_full + 8 * s);
+            }
+          }
         }
       }
     }
@@ -373,28 +383,30 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // ============================ MMA issuer ============================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc<kTf32>();
-      uint32_t it = 0, tile_iter = 0;
-      for (int i = cta; i < walk.total; i += num_ctas, ++tile_iter) {
-        const uint32_t acc = tile_iter & 1u;
-        wait_mbar(bar_tempty + 8 * acc, ((tile_iter >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty,
-                  tile_iter);
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % kStages;
-          wait_mbar(bar_full + 8 * s, (it / kStages) & 1u, timeout_ns, kTimeoutFullBar, it);
+      uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
+      for (int i = cta; i < walk.total; i += num_ctas) {
+        for (int seg = 0; seg < num_segs; ++seg, ++unit) {
+          const uint32_t acc = unit & 1u;
+          wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit);
           tc_fence_after();
-          const uint32_t sa = smem_base + s * kStageBytes;
-          const uint64_t adesc = make_smem_desc(sa);
-          const uint64_t bdesc = make_smem_desc(sa + kStageABytes);
+          const uint32_t d_tmem = tmem_base + acc * kBlockN;
+          const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
+          for (int kb = 0; kb < nkb; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            wait_mbar(bar_full + 8 * s, (it / kStages) & 1u, timeout_ns, kTimeoutFullBar, it);
+            tc_fence_after();
+            const uint32_t sa = smem_base + s * kStageBytes;
+            const uint64_t adesc = make_smem_desc(sa);
+            const uint64_t bdesc = make_smem_desc(sa + kStageABytes);
 #pragma unroll
-          for (int k = 0; k < kBlockKBytes / 32; ++k) {
-            // each MMA consumes 32 bytes of K; descriptors advance in 16-byte units
-            umma_ss<kTf32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockKBytes / 32; ++k) {
+              // each MMA consumes 32 bytes of K; descriptors advance in 16-byte units
+              umma_ss<kTf32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
           }
-          umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+          umma_commit(bar_tfull + 8 * acc);
         }
-        umma_commit(bar_tfull + 8 * acc);
       }
     }
   } else if (warp < 2 + kCommWarps) {
@@ -455,10 +467,43 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t stage_smem = smem_epi + q * kEpiWarpBytes;
     const int row = q * 32 + lane;  // row within the tile owned by this thread
-    uint32_t tile_iter = 0;
+    uint32_t unit = 0;  // (tile, K segment) counter, in step with the MMA warp
     const bool fused = (P.mode == kRS || P.mode == kAR) && P.world > 1;
-    for (int i = cta; i < walk.total; i += num_ctas, ++tile_iter) {
+    // running fp32 sums of this thread's row: [chunk][row][32 floats], private to the CTA
+    float* my_scratch = P.scratch == nullptr ? nullptr
+        : P.scratch + (static_cast<size_t>(blockIdx.x) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
+    for (int i = cta; i < walk.total; i += num_ctas) {
       const Tile t = walk.at(i);
+      // every segment but the last is only folded into the running sum
+      for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) {
+        const uint32_t sacc = unit & 1u;
+        if (lane == 0)
+          wait_mbar(bar_tfull + 8 * sacc, (unit >> 1) & 1u, timeout_ns, kTimeoutTmemFull, unit);
+        __syncwarp();
+        tc_fence_after();
+        const uint32_t staddr = tmem_base + sacc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld_32x32(staddr + c * 32, raw);
+          tmem_ld_wait();
+          float4* sp = reinterpret_cast<float4*>(my_scratch + static_cast<size_t>(c) * kBlockM * 32);
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            float4 x = make_float4(__uint_as_float(raw[4 * w]), __uint_as_float(raw[4 * w + 1]),
+                                   __uint_as_float(raw[4 * w + 2]), __uint_as_float(raw[4 * w + 3]));
+            if (seg > 0) {
+              const float4 y = sp[w];
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+            sp[w] = x;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * sacc);
+      }
+      const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
       const bool mine = (t.owner == P.rank);
       const bool reduce = fused && mine;
@@ -521,6 +566,18 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          }
+          if (num_segs > 1) {
+            // add the running sum of the earlier K segments (written by this same thread)
+            const float4* sp = reinterpret_cast<const float4*>(my_scratch + static_cast<size_t>(c) * kBlockM * 32);
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+              const float4 y = sp[w];
+              raw[4 * w] = __float_as_uint(__uint_as_float(raw[4 * w]) + y.x);
+              raw[4 * w + 1] = __float_as_uint(__uint_as_float(raw[4 * w + 1]) + y.y);
+              raw[4 * w + 2] = __float_as_uint(__uint_as_float(raw[4 * w + 2]) + y.z);
+              raw[4 * w + 3] = __float_as_uint(__uint_as_float(raw[4 * w + 3]) + y.w);
+            }
           }
           float v[32];
           if (reduce) {

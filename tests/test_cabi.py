@@ -36,7 +36,7 @@ def test_argument_validation_without_device(native_lib):
     assert native_lib.edm_gemm_bf16(None, 8, None, 8, None, 8, 8, 8, 8, None) == _lib.EDM_ERR_BAD_ARG
     assert native_lib.edm_gemm_bf16(16, 8, 16, 8, 16, 8, 0, 8, 8, None) == _lib.EDM_ERR_BAD_ARG
     assert native_lib.edm_gemm_fp32_workspace_bytes(0, 1, 1) == 0
-    assert native_lib.edm_gemm_fp32_workspace_bytes(256, 1024, 512) == 2 * 4 * (256 * 512 + 1024 * 512)
+    assert native_lib.edm_gemm_fp32_workspace_bytes(256, 1024, 512) == 2 * 4 * (256 * 512 + 1024 * 512) + 256 * 128 * 256 * 4
     assert native_lib.edm_set_timeout_ms(0) == _lib.EDM_ERR_BAD_ARG
     out = C.c_void_p()
     assert native_lib.edm_comm_create(3, 2, 1 << 20, 1 << 20, C.byref(out)) == _lib.EDM_ERR_BAD_ARG
