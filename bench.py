@@ -1,0 +1,371 @@
+"""Benchmark of the fused tensor-parallel linear path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens M]
+
+Workload (one "step" = one layer): the four linears of a Llama-3-70B prefill layer with the
+per-rank extents of tensor parallelism 8 -- all-gather+GEMM for QKV (N=1280) and gate_up
+(N=7168) with K=8192, GEMM+reduce-scatter for o_proj (K=1024) and down_proj (K=3584) with
+N=8192 -- on M tokens (default 8192), bf16 with fp32 accumulation, synthetic inputs
+(activations ~N(0,1), weights ~N(0,0.02)).  On N GPUs the same per-rank extents run with the
+exchange across N ranks (weak scaling; N=8 is the reference configuration itself); on 1 GPU
+there is nothing to exchange and the step is the four GEMMs.
+
+Prints ONE JSON line on rank 0.  ``value`` is microseconds per layer, device-timed with CUDA
+events on the launching stream, maximum over ranks.  ``e2e`` is the same layer driven through
+the public operators from pinned host buffers: host->device copies of the step's activations
+and device->host copies of its outputs are inside the timed region (weights are parameters
+and stay resident).
+
+``--impl reference`` times the CPU restatement of the path (the oracle; the reference itself
+has no implementation of it) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, FFN, TP_REF = 8192, 28672, 8
+# name, op, K, N (per-rank extents at TP=8)
+LAYER_OPS = (
+    ("qkv", "ag_gemm", HIDDEN, 10240 // TP_REF),
+    ("gate_up", "ag_gemm", HIDDEN, 2 * FFN // TP_REF),
+    ("o_proj", "gemm_rs", HIDDEN // TP_REF, HIDDEN),
+    ("down", "gemm_rs", FFN // TP_REF, HIDDEN),
+)
+NVLINK_GBS_NOMINAL = 900.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu
+# capture summarised in profiles/ (None until a capture of this workload exists)
+NCU_TRAFFIC_BYTES_PER_STEP = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def op_flops(M, K, N):
+    return 2.0 * M * K * N
+
+
+def nvlink_bytes(op, M, K, N, world):
+    if world <= 1:
+        return 0.0
+    frac = (world - 1) / world
+    return frac * M * (K if op == "ag_gemm" else N) * 2.0
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6:
+                continue
+            try:
+                sm.append(float(cells[0])); mx.append(float(cells[1]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, cells[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        # "under load" = the upper half of the samples (idle gaps between phases pull clocks down)
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU arm (oracle port)
+def cpu_layer_us(M: int, sample_rows: int, threads: int) -> tuple[float, str]:
+    """One rank's four GEMMs of the layer on the host cores (fp32 torch CPU matmul over bf16-rounded
+    inputs, i.e. the oracle's arithmetic at the speed of the host BLAS), timed on `sample_rows` of
+    the M tokens and scaled to M."""
+    import torch
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator(device="cpu").manual_seed(1234)
+    total = 0.0
+    for _name, _op, K, N in LAYER_OPS:
+        a = torch.randn(sample_rows, K, generator=gen).bfloat16().float()
+        b = (torch.randn(N, K, generator=gen) * 0.02).bfloat16().float()
+        torch.matmul(a[:64], b.t())  # warm the BLAS threads
+        t0 = time.perf_counter()
+        torch.matmul(a, b.t())
+        total += time.perf_counter() - t0
+    return total * 1e6 * (M / sample_rows), f"{sample_rows} of {M} token rows, 4 GEMMs, fp32 CPU matmul, scaled x{M / sample_rows:g}"
+
+
+def selector_sweep_us() -> float:
+    """The reference-style selector sweep (pure Python critical-path evaluation) over {1,2,4,8}."""
+    from oracle import cost_model
+
+    p = {"gemm_total": 294_000, "comm_bytes": 117_440_512, "alpha": 2_000, "beta_num": 1000, "beta_den": 770,
+         "split_overhead": 1_500, "comm_first": 0}
+    t0 = time.perf_counter()
+    for _ in range(20):
+        cost_model.select_schedule(p, [1, 2, 4, 8])
+    return (time.perf_counter() - t0) / 20 * 1e6
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    M = args.tokens
+    sample = min(M, 1024)
+    for _ in range(max(args.warmup, 0) and 1):
+        cpu_layer_us(M, 128, threads)
+    vals = []
+    for _ in range(max(1, min(args.steps, 5))):
+        v, desc = cpu_layer_us(M, sample, threads)
+        vals.append(v)
+    value = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": "fused_tp_layer_time", "value": value, "unit": "us/layer",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(M, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "us/layer", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(M: int, world: int) -> dict:
+    return {"workload": "llama3-70b prefill layer, tp8-local extents: AG+GEMM qkv(K8192,N1280) gate_up(K8192,N7168); "
+                        "GEMM+RS o_proj(K1024,N8192) down(K3584,N8192)",
+            "tokens": M, "tp": world,
+            "l2": "operands of one step (~0.35 GB) exceed the 126 MB L2; no explicit flush"}
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from edmir_b200 import linear, symm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M = args.tokens
+    assert M % (128 * max(world, 1)) == 0, "tokens must split into 128-row blocks per rank"
+    peaks, peak_src = load_peaks()
+
+    gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    ctx = None
+    if world > 1:
+        ctx = symm.SymmetricContext.create(symm.default_window_bytes(M, HIDDEN, HIDDEN, world), 1 << 20)
+
+    ops = []
+    for name, op, K, N in LAYER_OPS:
+        rows_in = M // world if op == "ag_gemm" else M
+        rows_out = M // world if op == "gemm_rs" else M
+        a_host = torch.randn(rows_in, K, generator=gen).to(torch.bfloat16).pin_memory()
+        b = (torch.randn(N, K, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+        ops.append({"name": name, "op": op, "K": K, "N": N, "a_host": a_host, "a": a_host.to(dev), "b": b,
+                    "out": torch.empty(rows_out, N, dtype=torch.bfloat16, device=dev),
+                    "out_host": torch.empty(rows_out, N, dtype=torch.bfloat16).pin_memory()})
+
+    def launch(o):
+        if world == 1:
+            linear.gemm(o["a"], o["b"], o["out"])
+        elif o["op"] == "ag_gemm":
+            ctx.ag_gemm(o["a"], o["b"], o["out"], chunks=args.chunks)
+        else:
+            ctx.gemm_rs(o["a"], o["b"], o["out"])
+
+    def layer():
+        for o in ops:
+            launch(o)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps * 1e3  # us per call
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    layer_us = timed(layer, args.steps, max(args.warmup, 3))
+
+    # per-op times (same launches, timed one op at a time)
+    per_op = []
+    sub_steps = max(10, args.steps // 4)
+    for o in ops:
+        us = timed(lambda o=o: launch(o), sub_steps, 3)
+        fl = op_flops(M, o["K"], o["N"])
+        wire = nvlink_bytes(o["op"], M, o["K"], o["N"], world)
+        roof_us = max(fl / (peaks["bf16_tflops"] * 1e12), wire / (NVLINK_GBS_NOMINAL * 1e9)) * 1e6
+        per_op.append({"name": o["name"], "op": o["op"] if world > 1 else "gemm", "us": round(us, 2),
+                       "tflops": round(fl / us / 1e6, 1), "roofline_us": round(roof_us, 2),
+                       "roofline_frac": round(roof_us / us, 4),
+                       "binds": "nvlink" if wire / (NVLINK_GBS_NOMINAL * 1e9) > fl / (peaks["bf16_tflops"] * 1e12) else "tensor"})
+
+    # comparison baselines measured in the same run
+    extra = {}
+    def unfused_layer():
+        for o in ops:
+            if world == 1:
+                torch.matmul(o["a"], o["b"].t(), out=o["out"])
+            elif o["op"] == "ag_gemm":
+                dist.all_gather_into_tensor(o["xg"], o["a"])
+                torch.matmul(o["xg"], o["b"].t(), out=o["out"])
+            else:
+                torch.matmul(o["a"], o["b"].t(), out=o["full"])
+                dist.reduce_scatter_tensor(o["out"], o["full"])
+    def gemm_only_layer():
+        for o in ops:
+            if o["op"] == "ag_gemm":
+                linear.gemm(o["xg"], o["b"], o["out"])
+            else:
+                linear.gemm(o["a"], o["b"], o["full"])
+    if world > 1:
+        for o in ops:
+            if o["op"] == "ag_gemm":
+                o["xg"] = torch.empty(M, o["K"], dtype=torch.bfloat16, device=dev)
+            else:
+                o["full"] = torch.empty(M, o["N"], dtype=torch.bfloat16, device=dev)
+        extra["unfused_matmul_nccl_us"] = round(timed(unfused_layer, sub_steps, 3), 2)
+        extra["gemm_only_us"] = round(timed(gemm_only_layer, sub_steps, 3), 2)
+        extra["exposed_comm_us"] = round(layer_us - extra["gemm_only_us"], 2)
+        def comm_only():
+            for o in ops:
+                if o["op"] == "ag_gemm":
+                    dist.all_gather_into_tensor(o["xg"], o["a"])
+                else:
+                    dist.reduce_scatter_tensor(o["out"], o["full"])
+        extra["nccl_collectives_only_us"] = round(timed(comm_only, sub_steps, 3), 2)
+        if extra["nccl_collectives_only_us"] > 0:
+            extra["exposed_comm_frac_of_collective"] = round(
+                max(extra["exposed_comm_us"], 0.0) / extra["nccl_collectives_only_us"], 4)
+    else:
+        extra["cublas_matmul_us"] = round(timed(unfused_layer, sub_steps, 3), 2)
+
+    # end to end from pinned host buffers
+    def e2e_step():
+        for o in ops:
+            o["a"].copy_(o["a_host"], non_blocking=True)
+            launch(o)
+            o["out_host"].copy_(o["out"], non_blocking=True)
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_us = timed(e2e_step, e2e_steps, 3)
+    h2d = sum(o["a_host"].numel() * 2 for o in ops)
+    d2h = sum(o["out_host"].numel() * 2 for o in ops)
+    clocks = sampler.stop() if sampler else None
+
+    status = linear.status()
+    assert status[0] == 0, f"device-side wait timed out: {status[:8]}"
+
+    if rank == 0:
+        flops = sum(op_flops(M, o["K"], o["N"]) for o in ops)
+        achieved = flops / layer_us / 1e6  # TFLOP/s per GPU
+        line = {
+            "metric": "fused_tp_layer_time", "value": round(layer_us, 2), "unit": "us/layer", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(layer_us / 1e3, 5),
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(M, world),
+            "tflops_per_gpu": round(achieved, 1), "tflops_total": round(achieved * world, 1),
+            "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
+                         "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4),
+                         "peak_source": f"{peak_src} (cuBLAS bf16 burst)", "kernel": "tp_gemm_kernel<bf16>",
+                         "traffic": NCU_TRAFFIC_BYTES_PER_STEP},
+            "per_op": per_op,
+            "e2e": {"value": round(e2e_us, 2), "unit": "us/layer", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * len(ops),
+            "clocks": clocks,
+        }
+        line.update(extra)
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            v, desc = cpu_layer_us(M, min(M, 1024), threads)
+            line["cpu_baseline"] = {"value": round(v, 1), "unit": "us/layer", "cores": threads, "kind": "port",
+                                    "sample": desc, "selector_sweep_us": round(selector_sweep_us(), 1)}
+        print(json.dumps(line), flush=True)
+
+    if ctx is not None:
+        sync_all()
+        ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--chunks", type=int, default=4, help="all-gather chunks per shard")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
