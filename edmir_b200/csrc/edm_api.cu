@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -74,28 +75,93 @@ int num_sms() {
   return n;
 }
 
-template <bool kTf32, typename OutT>
-int launch_kernel(const LaunchParams& lp, int grid, bool cooperative, cudaStream_t stream) {
-  auto kern = tp_gemm_kernel<kTf32, OutT>;
-  static bool configured = false;  // one flag per instantiation
-  if (!configured) {
-    EDM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    configured = true;
+// One launch path for every variant: plain, cooperative (emulated ranks must be co-resident),
+// and/or as clusters of 2 (CTA pairs).
+template <int kCG, bool kTf32, typename OutT>
+struct Variant {
+  static void* fn() { return reinterpret_cast<void*>(&tp_gemm_kernel<kCG, kTf32, OutT>); }
+  static int configure() {
+    static bool done = false;
+    if (!done) {
+      EDM_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      done = true;
+    }
+    return EDM_OK;
   }
-  if (cooperative) {
+  // Number of CTAs that can be resident at once (whole pairs for kCG == 2).
+  static int max_resident(int sms, int* out) {
+    static int cached = 0;
+    if (!cached) {
+      int rc = configure();
+      if (rc) return rc;
+      if (kCG == 1) {
+        cached = sms;
+      } else {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sms - sms % 2); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int clusters = 0;
+        EDM_CUDA(cudaOccupancyMaxActiveClusters(&clusters, fn(), &cfg));
+        cached = 2 * clusters;
+        if (cached > sms - sms % 2) cached = sms - sms % 2;
+        if (cached <= 0) return EDM_ERR_CUDA;
+      }
+    }
+    *out = cached;
+    return EDM_OK;
+  }
+  static int launch(const LaunchParams& lp, int grid, bool cooperative, cudaStream_t stream) {
+    int rc = configure();
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (kCG == 2) {
+      at[n].id = cudaLaunchAttributeClusterDimension;
+      at[n].val.clusterDim.x = 2; at[n].val.clusterDim.y = 1; at[n].val.clusterDim.z = 1;
+      ++n;
+    }
+    if (cooperative) {
+      at[n].id = cudaLaunchAttributeCooperative;
+      at[n].val.cooperative = 1;
+      ++n;
+    }
+    cfg.attrs = at; cfg.numAttrs = n;
     void* args[1] = {const_cast<LaunchParams*>(&lp)};
-    EDM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), dim3(grid), dim3(kThreads),
-                                         args, kSmemBytes, stream));
-  } else {
-    kern<<<grid, kThreads, kSmemBytes, stream>>>(lp);
-    EDM_CUDA(cudaGetLastError());
+    EDM_CUDA(cudaLaunchKernelExC(&cfg, fn(), args));
+    return EDM_OK;
   }
+};
+
+int launch_variant(int dtype, int cg, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
+  if (dtype == EDM_DTYPE_BF16) {
+    if (cg == 2) return Variant<2, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
+    return Variant<1, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
+  }
+  return Variant<1, true, float>::launch(lp, grid, coop, stream);
+}
+
+int max_resident_ctas(int dtype, int cg, int sms, int* out) {
+  if (dtype == EDM_DTYPE_BF16 && cg == 2) return Variant<2, false, __nv_bfloat16>::max_resident(sms, out);
+  *out = sms;
   return EDM_OK;
 }
 
-int launch_dtype(int dtype, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
-  if (dtype == EDM_DTYPE_BF16) return launch_kernel<false, __nv_bfloat16>(lp, grid, coop, stream);
-  return launch_kernel<true, float>(lp, grid, coop, stream);
+// CTA pairs pay off once there are whole 256-row tiles; EDM_CTA_GROUP=1|2 forces a variant.
+int pick_cta_group(int dtype, int op, int64_t M, int world) {
+  if (dtype != EDM_DTYPE_BF16) return 1;
+  int want = M >= 256 ? 2 : 1;
+  if (const char* e = std::getenv("EDM_CTA_GROUP")) {
+    if (e[0] == '1') want = 1;
+    if (e[0] == '2') want = 2;
+  }
+  if (want == 2 && op == EDM_OP_GEMM_RS && world > 1 && (M / world) % (2 * kBlockM) != 0) want = 1;
+  return want;
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -111,7 +177,8 @@ size_t split_ws_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 // Fills tmap_a/tmap_b (and runs the tf32 split for fp32) for a GEMM A[M,K] x B[N,K].
-int prepare_operands(RankParams& P, int dtype, const void* a, int64_t lda, int64_t a_rows,
+// `cg` = CTAs sharing a tile: each loads kBlockN / cg rows of the B tile per stage.
+int prepare_operands(RankParams& P, int dtype, int cg, const void* a, int64_t lda, int64_t a_rows,
                      const void* b, int64_t ldb, int64_t N, int64_t K, void* ws, size_t ws_bytes,
                      cudaStream_t stream) {
   if (dtype == EDM_DTYPE_BF16) {
@@ -119,7 +186,7 @@ int prepare_operands(RankParams& P, int dtype, const void* a, int64_t lda, int64
     int rc = make_tmap(&P.tmap_a[0], a, a_rows, K, lda, 2, kBlockM);
     if (rc) return rc;
     P.tmap_a[1] = P.tmap_a[0];
-    rc = make_tmap(&P.tmap_b[0], b, N, K, ldb, 2, kBlockN);
+    rc = make_tmap(&P.tmap_b[0], b, N, K, ldb, 2, kBlockN / cg);
     if (rc) return rc;
     P.tmap_b[1] = P.tmap_b[0];
     P.passes = 1;
@@ -142,8 +209,8 @@ int prepare_operands(RankParams& P, int dtype, const void* a, int64_t lda, int64
   int rc;
   if ((rc = make_tmap(&P.tmap_a[0], a_hi, a_rows, K, K, 4, kBlockM))) return rc;
   if ((rc = make_tmap(&P.tmap_a[1], a_lo, a_rows, K, K, 4, kBlockM))) return rc;
-  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN))) return rc;
-  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN / cg))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN / cg))) return rc;
   P.passes = 3;
   P.seg_kblocks = kSegKBlocks;
   P.scratch = reinterpret_cast<float*>(w + 2 * a_sz + 2 * b_sz);
@@ -168,19 +235,22 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   std::memset(&lp, 0, sizeof(lp));
   RankParams& P = lp.r[0];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  rc = prepare_operands(P, dtype, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
+  const int cg = pick_cta_group(dtype, EDM_OP_GEMM, M, 1);
+  rc = prepare_operands(P, dtype, cg, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
   if (rc) return rc;
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
   P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
   P.out = d; P.ld_out = ldd;
-  const int tiles = static_cast<int>(((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN));
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
-  const int grid = tiles < sms ? tiles : sms;
+  int resident = 0;
+  if ((rc = max_resident_ctas(dtype, cg, sms, &resident))) return rc;
+  const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + kBlockN - 1) / kBlockN));
+  const int grid = tiles * cg < resident ? tiles * cg : resident;
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
-  return launch_dtype(dtype, lp, grid, false, s);
+  return launch_variant(dtype, cg, lp, grid, false, s);
 }
 
 }  // namespace
@@ -216,9 +286,10 @@ struct Layout {
   size_t window_need = 0;
 };
 
-int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int elem_bytes, Layout& L) {
+int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int elem_bytes, int cg, Layout& L) {
   const int W = c->world;
-  L.m_blocks = (call.M + kBlockM - 1) / kBlockM;
+  const int tile_m = kBlockM * cg;  // a CTA pair schedules 256-row tiles; slots and flags stay per 128 rows
+  L.m_blocks = (call.M + tile_m - 1) / tile_m;
   L.n_blocks = (call.N + kBlockN - 1) / kBlockN;
   L.total = L.m_blocks * L.n_blocks;
   if (L.total > (1 << 24)) return EDM_ERR_BAD_ARG;
@@ -226,16 +297,16 @@ int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int
   if (call.op == EDM_OP_GEMM_RS) {
     if (call.M % W) return EDM_ERR_BAD_ARG;
     const int64_t rows = call.M / W;
-    if (rows % kBlockM) return EDM_ERR_UNSUPPORTED;  // row blocks must not straddle owners
-    L.max_owned = static_cast<int32_t>(rows / kBlockM * L.n_blocks);
+    if (rows % tile_m) return EDM_ERR_UNSUPPORTED;  // tiles must not straddle owners
+    L.max_owned = static_cast<int32_t>(rows / tile_m * L.n_blocks) * cg;
     L.window_need = tile_bytes * L.max_owned * W;
     L.flag_words = static_cast<uint32_t>(W) * L.max_owned * 4;
   } else if (call.op == EDM_OP_GEMM_AR) {
-    L.max_owned = static_cast<int32_t>((L.total + W - 1) / W);
+    L.max_owned = static_cast<int32_t>((L.total + W - 1) / W) * cg;
     L.window_need = tile_bytes * L.max_owned * W;
     L.partial_off = 0;
     L.result_off = static_cast<uint32_t>(W) * L.max_owned * 4;
-    L.flag_words = L.result_off + static_cast<uint32_t>(L.total) * 4;
+    L.flag_words = L.result_off + static_cast<uint32_t>(L.total) * cg * 4;
   } else if (call.op == EDM_OP_AG_GEMM) {
     if (call.M % W || call.chunks < 1 || call.chunks > 4096 || call.chunks > call.M / W)
       return EDM_ERR_BAD_ARG;
@@ -252,7 +323,7 @@ int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int
 }
 
 // Builds one rank's kernel parameters; bumps the context epoch.
-int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cudaStream_t stream) {
+int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams& P, cudaStream_t stream) {
   if (!c || !call.a || !call.b || !call.d) return EDM_ERR_BAD_ARG;
   int rc = check_dims(call.M, call.N, call.K);
   if (rc) return rc;
@@ -276,14 +347,14 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cud
     if (call.op == EDM_OP_GEMM_AR || call.op == EDM_OP_GEMM_RS || call.op == EDM_OP_GEMM ||
         call.op == EDM_OP_AG_GEMM) {
       P.mode = kPlain; P.epoch = 1;
-      return prepare_operands(P, call.dtype, call.a, call.lda, call.M, call.b, call.ldb, call.N,
+      return prepare_operands(P, call.dtype, cg, call.a, call.lda, call.M, call.b, call.ldb, call.N,
                               call.K, call.workspace, call.workspace_bytes, stream);
     }
     return EDM_ERR_BAD_ARG;
   }
 
   Layout L;
-  rc = plan_layout(c, call, out_bytes, elem_bytes, L);
+  rc = plan_layout(c, call, out_bytes, elem_bytes, cg, L);
   if (rc) return rc;
 
   const uint32_t epoch = c->epoch + 1;
@@ -314,7 +385,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cud
     // covers whole row blocks
     if ((rc = make_tmap(&P.tmap_a[0], P.gather[c->rank], call.M, call.K, call.K, 2, kBlockM))) return rc;
     if ((rc = make_tmap(&P.tmap_a[1], call.a, rows, call.K, call.lda, 2, kBlockM))) return rc;
-    if ((rc = make_tmap(&P.tmap_b[0], call.b, call.N, call.K, call.ldb, 2, kBlockN))) return rc;
+    if ((rc = make_tmap(&P.tmap_b[0], call.b, call.N, call.K, call.ldb, 2, kBlockN / cg))) return rc;
     P.tmap_b[1] = P.tmap_b[0];
   } else {
     P.mode = call.op == EDM_OP_GEMM_RS ? kRS : kAR;
@@ -327,7 +398,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cud
       const size_t off = static_cast<size_t>(d - c->base[c->rank]);
       for (int p = 0; p < W; ++p) P.peer_out[p] = c->base[p] + off;
     }
-    rc = prepare_operands(P, call.dtype, call.a, call.lda, call.M, call.b, call.ldb, call.N, call.K,
+    rc = prepare_operands(P, call.dtype, cg, call.a, call.lda, call.M, call.b, call.ldb, call.N, call.K,
                           call.workspace, call.workspace_bytes, stream);
     if (rc) return rc;
   }
@@ -335,10 +406,10 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, RankParams& P, cud
   return EDM_OK;
 }
 
-int grid_for(const RankParams& P, int sms) {
-  if (P.mode == kAG) return sms;  // push warps of every CTA help move the shard
-  const int tiles = ((P.M + kBlockM - 1) / kBlockM) * ((P.N + kBlockN - 1) / kBlockN);
-  return tiles < sms ? tiles : sms;
+int grid_for(const RankParams& P, int cg, int resident) {
+  if (P.mode == kAG) return resident;  // push warps of every CTA help move the shard
+  const int tiles = ((P.M + kBlockM * cg - 1) / (kBlockM * cg)) * ((P.N + kBlockN - 1) / kBlockN);
+  return tiles * cg < resident ? tiles * cg : resident;
 }
 }  // namespace
 
@@ -461,15 +532,18 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc = build_rank_params(comm, *call, lp.r[0], s);
+  const int cg = pick_cta_group(call->dtype, call->op, call->M, comm->world);
+  int rc = build_rank_params(comm, *call, cg, lp.r[0], s);
   if (rc) return rc;
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
-  const int grid = grid_for(lp.r[0], sms);
+  int resident = 0;
+  if ((rc = max_resident_ctas(call->dtype, cg, sms, &resident))) return rc;
+  const int grid = grid_for(lp.r[0], cg, resident);
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
-  return launch_dtype(call->dtype, lp, grid, false, s);
+  return launch_variant(call->dtype, cg, lp, grid, false, s);
 }
 
 int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls, int n, void* stream) {
@@ -477,17 +551,25 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int cg = pick_cta_group(calls[0].dtype, calls[0].op, calls[0].M, comms[0] ? comms[0]->world : 1);
   for (int i = 0; i < n; ++i) {
-    if (!comms[i] || calls[i].dtype != calls[0].dtype) return EDM_ERR_BAD_ARG;
-    int rc = build_rank_params(comms[i], calls[i], lp.r[i], s);
+    if (!comms[i] || calls[i].dtype != calls[0].dtype || calls[i].op != calls[0].op ||
+        calls[i].M != calls[0].M)
+      return EDM_ERR_BAD_ARG;
+    int rc = build_rank_params(comms[i], calls[i], cg, lp.r[i], s);
     if (rc) return rc;
   }
   const int sms = num_sms();
   if (sms < n) return EDM_ERR_CUDA;
+  int resident = 0;
+  int rc = max_resident_ctas(calls[0].dtype, cg, sms, &resident);
+  if (rc) return rc;
   lp.num_vranks = n;
-  lp.ctas_per_vrank = sms / n;  // all CTAs co-resident: the emulated ranks wait on one another
+  // all CTAs co-resident (the emulated ranks wait on one another); whole pairs per rank
+  lp.ctas_per_vrank = resident / n / cg * cg;
+  if (lp.ctas_per_vrank < cg) return EDM_ERR_CUDA;
   lp.timeout_ns = g_timeout_ns;
-  return launch_dtype(calls[0].dtype, lp, lp.ctas_per_vrank * n, true, s);
+  return launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
 }
 
 static int tp_bf16(edm_comm_t* comm, int op, const void* a, int64_t lda, const void* b, int64_t ldb,

@@ -29,18 +29,17 @@ namespace edm {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockKBytes = 128;  // one 128B swizzle row of K per stage
-constexpr int kStages = 4;
+constexpr int kPipeBytes = 192 * 1024;  // operand ring: 4 stages of 48 KiB, or 6 of 32 KiB for CTA pairs
 constexpr int kThreads = 256;
 constexpr int kMaxRanks = 8;
 constexpr int kMaxVirtualRanks = 4;
 constexpr int kCommWarps = 2;
 constexpr int kTmemCols = 512;
 constexpr int kStageABytes = kBlockM * kBlockKBytes;  // 16 KiB
-constexpr int kStageBBytes = kBlockN * kBlockKBytes;  // 32 KiB
-constexpr int kStageBytes = kStageABytes + kStageBBytes;
+constexpr int kMaxStages = 6;
 constexpr int kEpiRowBytes = 256;                      // staging row per pass
 constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;       // 8 KiB per epilogue warp
-constexpr int kSmemBytes = kStages * kStageBytes + 4 * kEpiWarpBytes + 1024 /*align*/ + 256;
+constexpr int kSmemBytes = kPipeBytes + 4 * kEpiWarpBytes + 1024 /*align*/ + 256;
 
 enum Mode : int32_t { kPlain = 0, kRS = 1, kAR = 2, kAG = 3 };
 
@@ -167,14 +166,15 @@ struct TileWalk {
   int m_blocks, n_blocks, total;
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
 
-  __device__ TileWalk(const RankParams& p) {
+  // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
+  __device__ TileWalk(const RankParams& p, int tile_m) {
     mode = p.mode; rank = p.rank; world = p.world;
-    m_blocks = (p.M + kBlockM - 1) / kBlockM;
+    m_blocks = (p.M + tile_m - 1) / tile_m;
     n_blocks = (p.N + kBlockN - 1) / kBlockN;
     total = m_blocks * n_blocks;
     const int rows_per_rank = p.M / max(world, 1);
-    mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % kBlockM == 0)
-                      ? rows_per_rank / kBlockM : 0;
+    mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % tile_m == 0)
+                      ? rows_per_rank / tile_m : 0;
   }
 
   __device__ Tile at(int i) const {
@@ -231,12 +231,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
   return d;
 }
-template <bool kTf32>
+template <int kCG, bool kTf32>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   const uint32_t fmt = kTf32 ? 2u : 1u;  // 1 = BF16, 2 = TF32
   return (1u << 4)                        // D format F32
          | (fmt << 7) | (fmt << 10)       // A, B formats; both K-major (bits 15,16 = 0)
-         | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+         | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>((kBlockM * kCG) >> 4) << 24);
 }
 
 // ------------------------------------------------------------------ output conversion
@@ -267,9 +267,17 @@ template <> struct OutPack<float> {
 };
 
 // ------------------------------------------------------------------ the kernel
-template <bool kTf32, typename OutT>
+// kCG = 1: one CTA per 128x256 tile.  kCG = 2: a CTA pair (cluster of 2) shares a 256x256 tile;
+// each CTA loads its 128 rows of A and its 128-row half of the B tile, the even CTA issues
+// cta_group::2 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its own
+// 128 accumulator rows, so the epilogue is the same per-CTA code in both variants.
+template <int kCG, bool kTf32, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
+  constexpr int kStageBBytes = (kBlockN / kCG) * kBlockKBytes;  // 32 KiB, or 16 KiB per CTA of a pair
+  constexpr int kStageBytes = kStageABytes + kStageBBytes;
+  constexpr int kStages = kPipeBytes / kStageBytes;             // 4 or 6
+  static_assert(kStages <= kMaxStages, "barrier array too small");
   constexpr int kElemBytes = kTf32 ? 4 : 2;
   constexpr int kBlockK = kBlockKBytes / kElemBytes;   // elements of K per stage
   constexpr int kOutBytes = sizeof(OutT);
@@ -281,12 +289,15 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[2 * kStages + 4];
+  __shared__ uint64_t bars[2 * kMaxStages + 4];
   __shared__ uint32_t tmem_base_slot;
 
   const int vr = blockIdx.x / lp.ctas_per_vrank;
-  const int cta = blockIdx.x - vr * lp.ctas_per_vrank;
-  const int num_ctas = lp.ctas_per_vrank;
+  const int cta_in_rank = blockIdx.x - vr * lp.ctas_per_vrank;
+  // scheduling unit: a CTA, or a CTA pair (ctas_per_vrank is even then and pairs never straddle ranks)
+  const int cta = cta_in_rank / kCG;
+  const int num_ctas = lp.ctas_per_vrank / kCG;
+  const uint32_t pr = kCG == 2 ? cluster_ctarank() : 0u;  // position in the pair; 0 issues the MMAs
   const RankParams& P = lp.r[vr];
   const uint64_t timeout_ns = lp.timeout_ns;
 
@@ -307,21 +318,22 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 4);
+      mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
     }
     mbar_fence_init();
     fence_proxy_async_smem();
   }
   if (warp == 2) {
-    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<kCG>(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish<kCG>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (kCG == 2) cluster_sync_all();  // partner's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P);
+  const TileWalk walk(P, kBlockM * kCG);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -338,8 +350,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       uint32_t it = 0;
       for (int i = cta; i < walk.total; i += num_ctas) {
         const Tile t = walk.at(i);
-        const int m0 = t.m_blk * kBlockM;
-        const int n0 = t.n_blk * kBlockN;
+        const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM;  // this CTA's rows of A
+        const int n0 = t.n_blk * kBlockN + static_cast<int>(pr) * (kBlockN / kCG);  // its rows of B
         const CUtensorMap* amap = &P.tmap_a[0];
         int a_row = m0;
         if (P.mode == kAG) {
@@ -370,10 +382,18 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             for (int j = j0; j < j1; ++j, ++it) {
               const uint32_t s = it % kStages;
               wait_mbar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
-              mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
               const uint32_t sa = smem_base + s * kStageBytes;
-              tma_load_2d(sa, am, j * kBlockK, a_row, bar_full + 8 * s);
-              tma_load_2d(sa + kStageABytes, bm, j * kBlockK, n0, bar_full + 8 * s);
+              if constexpr (kCG == 1) {
+                mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
+                tma_load_2d(sa, am, j * kBlockK, a_row, bar_full + 8 * s);
+                tma_load_2d(sa + kStageABytes, bm, j * kBlockK, n0, bar_full + 8 * s);
+              } else {
+                // both CTAs' loads complete on the even CTA's barrier, which expects both stages
+                if (pr == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kStageBytes);
+                const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
+                tma_load_2d_pair(sa, am, j * kBlockK, a_row, fb);
+                tma_load_2d_pair(sa + kStageABytes, bm, j * kBlockK, n0, fb);
+              }
             }
           }
         }
@@ -381,8 +401,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ============================
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<kTf32>();
+    if (lane == 0 && pr == 0) {
+      constexpr uint32_t idesc = make_idesc<kCG, kTf32>();
       uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
       for (int i = cta; i < walk.total; i += num_ctas) {
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
@@ -401,11 +421,14 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 #pragma unroll
             for (int k = 0; k < kBlockKBytes / 32; ++k) {
               // each MMA consumes 32 bytes of K; descriptors advance in 16-byte units
-              umma_ss<kTf32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_ss<kCG, kTf32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
             }
-            umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if constexpr (kCG == 1) umma_commit(bar_empty + 8 * s);
+            else umma_commit_pair(bar_empty + 8 * s, 3);
           }
-          umma_commit(bar_tfull + 8 * acc);
+          if constexpr (kCG == 1) umma_commit(bar_tfull + 8 * acc);
+          else umma_commit_pair(bar_tfull + 8 * acc, 3);
         }
       }
     }
@@ -413,8 +436,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // ============================ all-gather pushes ============================
     if (P.mode == kAG && P.world > 1) {
       const int cw = warp - 2;
-      const int gw = cta * kCommWarps + cw;
-      const int total_warps = num_ctas * kCommWarps;
+      const int gw = cta_in_rank * kCommWarps + cw;
+      const int total_warps = lp.ctas_per_vrank * kCommWarps;
       const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
       const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
       const int first_d = P.ag_local_direct ? 1 : 0;
@@ -474,6 +497,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         : P.scratch + (static_cast<size_t>(blockIdx.x) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
     for (int i = cta; i < walk.total; i += num_ctas) {
       const Tile t = walk.at(i);
+      // this CTA's 128-row half of the tile: its slot / flag index and its result-flag index
+      const int slot_idx = t.owned_idx * kCG + static_cast<int>(pr);
+      const int half_lin = t.linear * kCG + static_cast<int>(pr);
       // every segment but the last is only folded into the running sum
       for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) {
         const uint32_t sacc = unit & 1u;
@@ -501,7 +527,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * sacc);
+        if (lane == 0) {
+          if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * sacc);
+          else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * sacc, 0));
+        }
       }
       const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
@@ -513,8 +542,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         // partial tiles (this warp's quarter) from every other rank must have landed
         if (lane < P.world && lane != P.rank)
           wait_flag(P.flags[P.rank] + P.partial_flag_off +
-                        (static_cast<uint32_t>(lane) * P.max_owned + t.owned_idx) * 4 + q,
-                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | t.owned_idx);
+                        (static_cast<uint32_t>(lane) * P.max_owned + slot_idx) * 4 + q,
+                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | slot_idx);
         __syncwarp();
       }
       if (lane == 0)
@@ -523,7 +552,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       tc_fence_after();
 
       // destinations of this tile
-      const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
+      const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBlockN;
       const int valid_cols = min(kBlockN, P.N - n0);
       int valid_rows = min(kBlockM, P.M - m0);
       int ndst = 1;
@@ -531,7 +560,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       int64_t dst_ld;  // bytes
       if (push_partial) {
         dst_base[0] = P.win[t.owner] +
-                      (static_cast<int64_t>(P.rank) * P.max_owned + t.owned_idx) * kTileOutBytes;
+                      (static_cast<int64_t>(P.rank) * P.max_owned + slot_idx) * kTileOutBytes;
         dst_ld = kBlockN * kOutBytes;
         valid_rows = kBlockM;
       } else if (P.mode == kRS) {
@@ -565,7 +594,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             // accumulator fully read: hand the TMEM buffer back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            if (lane == 0) {
+              if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * acc);
+              else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+            }
           }
           if (num_segs > 1) {
             // add the running sum of the earlier K segments (written by this same thread)
@@ -590,7 +622,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                 for (int e = 0; e < 32; ++e) v[e] += __uint_as_float(raw[e]);
               } else {
                 const char* slot = P.win[P.rank] +
-                                   (static_cast<int64_t>(src) * P.max_owned + t.owned_idx) * kTileOutBytes +
+                                   (static_cast<int64_t>(src) * P.max_owned + slot_idx) * kTileOutBytes +
                                    static_cast<int64_t>(row) * (kBlockN * kOutBytes) + c * 32 * kOutBytes;
 #pragma unroll
                 for (int w = 0; w < 32 / kOutPerVec; ++w) {
@@ -646,14 +678,14 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         if (lane == 0) {
           fence_acq_rel_sys();
           st_release_sys(P.flags[t.owner] + P.partial_flag_off +
-                             (static_cast<uint32_t>(P.rank) * P.max_owned + t.owned_idx) * 4 + q,
+                             (static_cast<uint32_t>(P.rank) * P.max_owned + slot_idx) * 4 + q,
                          P.epoch);
         }
       } else if (P.mode == kAR && fused) {
         __syncwarp();
         if (lane < P.world && lane != P.rank) {
           fence_acq_rel_sys();
-          st_release_sys(P.flags[lane] + P.result_flag_off + static_cast<uint32_t>(t.linear) * 4 + q,
+          st_release_sys(P.flags[lane] + P.result_flag_off + static_cast<uint32_t>(half_lin) * 4 + q,
                          P.epoch);
         }
       }
@@ -661,11 +693,12 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 
     if (P.mode == kAR && fused) {
       // the call is complete on this rank only when every other owner's tiles have arrived
-      const int gw = cta * 4 + q;
-      const int total_warps = num_ctas * 4;
-      for (int base = gw * 32; base < walk.total * 4; base += total_warps * 32) {
-        const int idx = base + lane;  // (tile, quarter) pair
-        if (idx < walk.total * 4 && (idx >> 2) % P.world != P.rank)
+      const int gw = cta_in_rank * 4 + q;
+      const int total_warps = lp.ctas_per_vrank * 4;
+      const int nflags = walk.total * kCG * 4;  // (tile half, quarter) pairs
+      for (int base = gw * 32; base < nflags; base += total_warps * 32) {
+        const int idx = base + lane;
+        if (idx < nflags && ((idx >> 2) / kCG) % P.world != P.rank)
           wait_flag(P.flags[P.rank] + P.result_flag_off + idx, P.epoch, timeout_ns,
                     kTimeoutResultFlag, idx);
       }
@@ -676,9 +709,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_before();
   __syncthreads();
   if (aborted()) __nanosleep(200000);  // let loads that are still in flight land before smem goes away
+  // a pair leaves together: the partner may still signal this CTA's barriers or read its smem
+  if constexpr (kCG == 2) cluster_sync_all();
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<kCG>(tmem_base, kTmemCols);
   }
 }
 
