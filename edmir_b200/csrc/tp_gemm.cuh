@@ -146,6 +146,7 @@ struct Tile {
   int owner;      // rank that ends up holding / reducing this tile
   int owned_idx;  // index of the tile among the owner's tiles (slot / flag index)
   int linear;     // m_blk * n_blocks + n_blk
+  bool valid;     // false for a hole in the walk (all-reduce with a tile count not divisible by world)
 };
 
 // Walk an (mb x nb) grid in bands of 8 row-blocks so that concurrently running CTAs share
@@ -164,6 +165,7 @@ __device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n
 struct TileWalk {
   int mode, rank, world;
   int m_blocks, n_blocks, total;
+  int positions;    // length of the walk (>= total when it has holes)
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
@@ -175,34 +177,41 @@ struct TileWalk {
     const int rows_per_rank = p.M / max(world, 1);
     mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % tile_m == 0)
                       ? rows_per_rank / tile_m : 0;
+    positions = (mode == kAR && world > 1) ? (total + world - 1) / world * world : total;
+  }
+
+  // tiles owned by `r`
+  __device__ int owned_count(int r) const {
+    if (mode == kRS) return mb_per_rank * n_blocks;
+    if (mode == kAR && world > 1) return (total - r + world - 1) / world;
+    return total;
+  }
+  // coordinates of the idx-th tile owned by `r`
+  __device__ void owned_tile(int r, int idx, int& m_blk, int& n_blk) const {
+    if (mode == kRS) {
+      int lm;
+      band_order(idx, mb_per_rank, n_blocks, lm, n_blk);
+      m_blk = r * mb_per_rank + lm;
+    } else {
+      const int lin = idx * world + r;
+      m_blk = lin / n_blocks;
+      n_blk = lin - m_blk * n_blocks;
+    }
   }
 
   __device__ Tile at(int i) const {
     Tile t;
-    if (mode == kRS) {
-      // owners in the order rank+1, rank+2, ..., rank: peers' rows first, own rows last
-      const int per_owner = mb_per_rank * n_blocks;
-      const int d = i / per_owner;
-      t.owner = (rank + 1 + d) % world;
-      int lm, n;
-      band_order(i - d * per_owner, mb_per_rank, n_blocks, lm, n);
-      t.m_blk = t.owner * mb_per_rank + lm;
-      t.n_blk = n;
-      t.owned_idx = lm * n_blocks + n;
-    } else if (mode == kAR && world > 1) {
-      // tile `lin` belongs to rank lin % world; visit owners rank+1, ..., rank
-      int rem = i, o = rank, cnt = 0;
-      for (int d = 1; d <= world; ++d) {
-        o = (rank + d) % world;
-        cnt = (total - o + world - 1) / world;
-        if (rem < cnt) break;
-        rem -= cnt;
-      }
-      const int lin = rem * world + o;
-      t.owner = o;
-      t.owned_idx = rem;
-      t.m_blk = lin / n_blocks;
-      t.n_blk = lin % n_blocks;
+    t.valid = true;
+    if ((mode == kRS || mode == kAR) && world > 1) {
+      // Round R = i / world: this rank computes tile R of every owner, in the order rank+1,
+      // rank+2, ..., rank.  Pushes therefore leave at a steady rate towards every peer for the
+      // whole launch, and every owner receives the partials of its tile R from all ranks at
+      // about the same time.
+      const int round = i / world;
+      t.owner = (rank + 1 + (i - round * world)) % world;
+      t.owned_idx = round;
+      t.valid = round < owned_count(t.owner);
+      owned_tile(t.owner, round, t.m_blk, t.n_blk);
     } else if (mode == kAG && mb_per_rank > 0) {
       int pm, n;
       band_order(i, m_blocks, n_blocks, pm, n);
@@ -348,8 +357,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       tma_prefetch_desc(&P.tmap_a[0]);
       tma_prefetch_desc(&P.tmap_b[0]);
       uint32_t it = 0;
-      for (int i = cta; i < walk.total; i += num_ctas) {
+      for (int i = cta; i < walk.positions; i += num_ctas) {
         const Tile t = walk.at(i);
+        if (!t.valid) continue;
         const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM;  // this CTA's rows of A
         const int n0 = t.n_blk * kBlockN + static_cast<int>(pr) * (kBlockN / kCG);  // its rows of B
         const CUtensorMap* amap = &P.tmap_a[0];
@@ -404,7 +414,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     if (lane == 0 && pr == 0) {
       constexpr uint32_t idesc = make_idesc<kCG, kTf32>();
       uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
-      for (int i = cta; i < walk.total; i += num_ctas) {
+      for (int i = cta; i < walk.positions; i += num_ctas) {
+        if (!walk.at(i).valid) continue;
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
           const uint32_t acc = unit & 1u;
           wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit);
@@ -441,33 +452,38 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
       const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
       const int first_d = P.ag_local_direct ? 1 : 0;
-      for (int c = 0; c < P.ag_chunks; ++c) {
-        const int r_lo = c * chunk_rows;
-        const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
-        const int64_t nvec = static_cast<int64_t>(max(r_hi - r_lo, 0)) * row_vecs;
-        for (int d = first_d; d < P.world; ++d) {
-          const int peer = (P.rank - d + P.world) % P.world;  // rank-1 needs this shard first
-          const char* src = static_cast<const char*>(P.x_local);
-          char* dst = static_cast<char*>(P.gather[peer]);
-          const int64_t src_ld = P.ld_x * kElemBytes;
-          const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
-          const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
-          constexpr int kUnroll = 4;
+      // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after its
+      // own), then to rank-2, ...; every GPU sends to and receives from one peer at a time
+      for (int d = first_d; d < P.world; ++d) {
+        const int peer = (P.rank - d + P.world) % P.world;
+        const char* src = static_cast<const char*>(P.x_local);
+        char* dst = static_cast<char*>(P.gather[peer]);
+        const int64_t src_ld = P.ld_x * kElemBytes;
+        const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
+        const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
+        for (int c = 0; c < P.ag_chunks; ++c) {
+          const int r_lo = c * chunk_rows;
+          const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
+          const int64_t nvec = static_cast<int64_t>(max(r_hi - r_lo, 0)) * row_vecs;
+          constexpr int kUnroll = 8;
           for (int64_t v0 = static_cast<int64_t>(gw) * 32 * kUnroll; v0 < nvec;
                v0 += static_cast<int64_t>(total_warps) * 32 * kUnroll) {
             uint4 buf[kUnroll];
-            int64_t row[kUnroll], col[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
               const int64_t v = v0 + u * 32 + lane;
-              row[u] = v / row_vecs;
-              col[u] = v - row[u] * row_vecs;
-              if (v < nvec) buf[u] = ld_cg_v4(src + (r_lo + row[u]) * src_ld + col[u] * 16);
+              if (v < nvec) {
+                const int64_t row = v / row_vecs, col = v - row * row_vecs;
+                buf[u] = ld_cg_v4(src + (r_lo + row) * src_ld + col * 16);
+              }
             }
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
               const int64_t v = v0 + u * 32 + lane;
-              if (v < nvec) st_global_v4(dst + (dst_row0 + r_lo + row[u]) * dst_ld + col[u] * 16, buf[u]);
+              if (v < nvec) {
+                const int64_t row = v / row_vecs, col = v - row * row_vecs;
+                st_global_v4(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, buf[u]);
+              }
             }
           }
           __syncwarp();
@@ -485,21 +501,112 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         }
       }
     }
+    if ((P.mode == kRS || P.mode == kAR) && P.world > 1) {
+      // ============================ reducer ============================
+      // Adds up the W partial copies of every 128-row half-tile this rank owns (fp32, fixed rank
+      // order, so the result is deterministic) and writes the result: to the local output
+      // (reduce-scatter) or to every rank's output (all-reduce).  It runs beside the tile loop and
+      // never holds up the MMA pipeline; each of the two warps takes two of the four row quarters.
+      const int cw = warp - 2;
+      const int W = P.world;
+      const int n_items = walk.owned_count(P.rank) * kCG;  // half-tiles owned by this rank
+      constexpr int kU = 4;                                 // 16B vectors per lane in flight, per source
+      for (int item = cta_in_rank; item < n_items; item += lp.ctas_per_vrank) {
+        const int idx = item / kCG, hp = item - idx * kCG;  // owned tile, half within the pair tile
+        int m_blk, n_blk;
+        walk.owned_tile(P.rank, idx, m_blk, n_blk);
+        const int m0 = (m_blk * kCG + hp) * kBlockM, n0 = n_blk * kBlockN;
+        const int valid_rows = min(kBlockM, P.M - m0), valid_cols = min(kBlockN, P.N - n0);
+        const int64_t out_row0 = P.mode == kRS ? m0 - P.rank * rows_per_rank : m0;
+        const int64_t ld_bytes = P.ld_out * kOutBytes;
+        const char* slot0 = P.win[P.rank] + static_cast<int64_t>(item) * kTileOutBytes;
+        const int64_t src_stride = static_cast<int64_t>(P.max_owned) * kTileOutBytes;
+        for (int qq = 2 * cw; qq < 2 * cw + 2; ++qq) {
+          if (lane < W)
+            wait_flag(P.flags[P.rank] + P.partial_flag_off +
+                          (static_cast<uint32_t>(lane) * P.max_owned + item) * 4 + qq,
+                      P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | item);
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < kPasses; ++h) {
+            const char* blk = slot0 + (h * 4 + qq) * kEpiWarpBytes;  // 512 vectors of 16 B
+#pragma unroll 1
+            for (int it = 0; it < kEpiWarpBytes / 16 / 32; it += kU) {
+              uint4 x[kU][kMaxRanks];
+#pragma unroll
+              for (int u = 0; u < kU; ++u)
+#pragma unroll
+                for (int src = 0; src < kMaxRanks; ++src)
+                  if (src < W) x[u][src] = ld_cg_v4(blk + src * src_stride + ((it + u) * 32 + lane) * 16);
+#pragma unroll
+              for (int u = 0; u < kU; ++u) {
+                float sum[kOutPerVec];
+#pragma unroll
+                for (int e = 0; e < kOutPerVec; ++e) sum[e] = 0.f;
+#pragma unroll
+                for (int src = 0; src < kMaxRanks; ++src) {
+                  if (src < W) {
+                    if constexpr (kOutBytes == 2) {
+                      OutPack<__nv_bfloat16>::add16B(sum, x[u][src]);
+                    } else {
+                      sum[0] += __uint_as_float(x[u][src].x); sum[1] += __uint_as_float(x[u][src].y);
+                      sum[2] += __uint_as_float(x[u][src].z); sum[3] += __uint_as_float(x[u][src].w);
+                    }
+                  }
+                }
+                uint4 o;
+                if constexpr (kOutBytes == 2) {
+                  o = OutPack<__nv_bfloat16>::pack8(sum);
+                } else {
+                  o.x = __float_as_uint(sum[0]); o.y = __float_as_uint(sum[1]);
+                  o.z = __float_as_uint(sum[2]); o.w = __float_as_uint(sum[3]);
+                }
+                // undo the staging layout: vector -> (row, logical 16B vector)
+                const int vec = (it + u) * 32 + lane;
+                const int r = vec >> 4, lv = (vec & 15) ^ (r & 7);
+                const int trow = qq * 32 + r, col = h * kColsPerPass + lv * kOutPerVec;
+                if (trow < valid_rows && col < valid_cols) {
+                  const int64_t off = (out_row0 + trow) * ld_bytes + static_cast<int64_t>(n0 + col) * kOutBytes;
+                  if (P.mode == kRS) {
+                    st_global_v4(static_cast<char*>(P.out) + off, o);
+                  } else {
+#pragma unroll
+                    for (int d = 0; d < kMaxRanks; ++d)
+                      if (d < W) st_global_v4(static_cast<char*>(P.peer_out[(P.rank + d) % W]) + off, o);
+                  }
+                }
+              }
+            }
+          }
+          if (P.mode == kAR) {
+            // this quarter of the reduced half-tile now sits in every rank's output
+            __syncwarp();
+            if (lane < W && lane != P.rank) {
+              fence_acq_rel_sys();
+              const int lin = idx * W + P.rank;
+              st_release_sys(P.flags[lane] + P.result_flag_off +
+                                 static_cast<uint32_t>(lin * kCG + hp) * 4 + qq, P.epoch);
+            }
+          }
+        }
+      }
+    }
   } else {
     // ============================ epilogue ============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t stage_smem = smem_epi + q * kEpiWarpBytes;
     const int row = q * 32 + lane;  // row within the tile owned by this thread
     uint32_t unit = 0;  // (tile, K segment) counter, in step with the MMA warp
+    bool bulk_pending = false;  // a bulk copy out of this warp's staging rows may still be reading them
     const bool fused = (P.mode == kRS || P.mode == kAR) && P.world > 1;
     // running fp32 sums of this thread's row: [chunk][row][32 floats], private to the CTA
     float* my_scratch = P.scratch == nullptr ? nullptr
         : P.scratch + (static_cast<size_t>(blockIdx.x) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
-    for (int i = cta; i < walk.total; i += num_ctas) {
+    for (int i = cta; i < walk.positions; i += num_ctas) {
       const Tile t = walk.at(i);
-      // this CTA's 128-row half of the tile: its slot / flag index and its result-flag index
+      if (!t.valid) continue;
+      // this CTA's 128-row half of the tile: its slot / flag index at the owner
       const int slot_idx = t.owned_idx * kCG + static_cast<int>(pr);
-      const int half_lin = t.linear * kCG + static_cast<int>(pr);
       // every segment but the last is only folded into the running sum
       for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) {
         const uint32_t sacc = unit & 1u;
@@ -534,52 +641,23 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       }
       const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
-      const bool mine = (t.owner == P.rank);
-      const bool reduce = fused && mine;
-      const bool push_partial = fused && !mine;
-
-      if (reduce) {
-        // partial tiles (this warp's quarter) from every other rank must have landed
-        if (lane < P.world && lane != P.rank)
-          wait_flag(P.flags[P.rank] + P.partial_flag_off +
-                        (static_cast<uint32_t>(lane) * P.max_owned + slot_idx) * 4 + q,
-                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | slot_idx);
-        __syncwarp();
-      }
       if (lane == 0)
         wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter);
       __syncwarp();
       tc_fence_after();
 
-      // destinations of this tile
+      // Where the tile goes.  Fused modes: every tile -- this rank's own included -- is shipped
+      // as a partial into the owner's window slot [source rank][slot]; the owner's reducer warps
+      // add the slots up.  Otherwise it is written to the output in place.
       const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBlockN;
       const int valid_cols = min(kBlockN, P.N - n0);
-      int valid_rows = min(kBlockM, P.M - m0);
-      int ndst = 1;
-      char* dst_base[kMaxRanks];
-      int64_t dst_ld;  // bytes
-      if (push_partial) {
-        dst_base[0] = P.win[t.owner] +
-                      (static_cast<int64_t>(P.rank) * P.max_owned + slot_idx) * kTileOutBytes;
-        dst_ld = kBlockN * kOutBytes;
-        valid_rows = kBlockM;
-      } else if (P.mode == kRS) {
-        const int lm0 = m0 - P.rank * rows_per_rank;
-        dst_base[0] = static_cast<char*>(P.out) + (static_cast<int64_t>(lm0) * P.ld_out + n0) * kOutBytes;
-        dst_ld = P.ld_out * kOutBytes;
-      } else if (P.mode == kAR && fused) {
-        ndst = P.world;
-        for (int d = 0; d < P.world; ++d) {
-          const int peer = (P.rank + d) % P.world;  // own copy first
-          dst_base[d] = static_cast<char*>(P.peer_out[peer]) +
-                        (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
-        }
-        dst_ld = P.ld_out * kOutBytes;
-      } else {
-        dst_base[0] = static_cast<char*>(P.out) + (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
-        dst_ld = P.ld_out * kOutBytes;
-      }
-      const int push_cols = push_partial ? kBlockN : valid_cols;
+      const int valid_rows = min(kBlockM, P.M - m0);
+      char* dst_base;
+      if (fused)
+        dst_base = P.win[t.owner] + (static_cast<int64_t>(P.rank) * P.max_owned + slot_idx) * kTileOutBytes;
+      else
+        dst_base = static_cast<char*>(P.out) + (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
+      const int64_t dst_ld = P.ld_out * kOutBytes;
 
       const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
@@ -599,48 +677,27 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
               else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
             }
           }
+          float v[32];
           if (num_segs > 1) {
             // add the running sum of the earlier K segments (written by this same thread)
             const float4* sp = reinterpret_cast<const float4*>(my_scratch + static_cast<size_t>(c) * kBlockM * 32);
 #pragma unroll
             for (int w = 0; w < 8; ++w) {
               const float4 y = sp[w];
-              raw[4 * w] = __float_as_uint(__uint_as_float(raw[4 * w]) + y.x);
-              raw[4 * w + 1] = __float_as_uint(__uint_as_float(raw[4 * w + 1]) + y.y);
-              raw[4 * w + 2] = __float_as_uint(__uint_as_float(raw[4 * w + 2]) + y.z);
-              raw[4 * w + 3] = __float_as_uint(__uint_as_float(raw[4 * w + 3]) + y.w);
-            }
-          }
-          float v[32];
-          if (reduce) {
-            // fixed summation order over ranks keeps the result run-to-run deterministic
-#pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0.f;
-            for (int src = 0; src < P.world; ++src) {
-              if (src == P.rank) {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) v[e] += __uint_as_float(raw[e]);
-              } else {
-                const char* slot = P.win[P.rank] +
-                                   (static_cast<int64_t>(src) * P.max_owned + slot_idx) * kTileOutBytes +
-                                   static_cast<int64_t>(row) * (kBlockN * kOutBytes) + c * 32 * kOutBytes;
-#pragma unroll
-                for (int w = 0; w < 32 / kOutPerVec; ++w) {
-                  const uint4 x = ld_cg_v4(slot + w * 16);
-                  if constexpr (kOutBytes == 2) {
-                    OutPack<__nv_bfloat16>::add16B(&v[w * 8], x);
-                  } else {
-                    v[w * 4 + 0] += __uint_as_float(x.x);
-                    v[w * 4 + 1] += __uint_as_float(x.y);
-                    v[w * 4 + 2] += __uint_as_float(x.z);
-                    v[w * 4 + 3] += __uint_as_float(x.w);
-                  }
-                }
-              }
+              v[4 * w] = __uint_as_float(raw[4 * w]) + y.x;
+              v[4 * w + 1] = __uint_as_float(raw[4 * w + 1]) + y.y;
+              v[4 * w + 2] = __uint_as_float(raw[4 * w + 2]) + y.z;
+              v[4 * w + 3] = __uint_as_float(raw[4 * w + 3]) + y.w;
             }
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+          }
+          if (j == 0 && bulk_pending) {
+            // the previous pass's bulk copy may still be reading the staging rows
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+            bulk_pending = false;
           }
           // registers -> staging: thread owns row `lane`; 16B vectors XOR-swizzled by row
 #pragma unroll
@@ -656,36 +713,41 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             st_shared_v4(stage_smem + lane * kEpiRowBytes + ((lv ^ (lane & 7)) << 4), o);
           }
         }
+        if (fused) {
+          // ship the warp's 8 KiB of staged rows as they are with one bulk copy; a slot keeps the
+          // staging layout [pass][warp][row][swizzled 16B vectors]
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            bulk_store(dst_base + (h * 4 + q) * kEpiWarpBytes, stage_smem, kEpiWarpBytes);
+            bulk_commit();
+          }
+          bulk_pending = true;
+          continue;
+        }
         __syncwarp();
         // staging -> global: two full 256B rows per warp instruction
         const int col0 = h * kColsPerPass;  // first tile column of this pass
-        for (int d = 0; d < ndst; ++d) {
 #pragma unroll 4
-          for (int itr = 0; itr < 16; ++itr) {
-            const int lr = itr * 2 + (lane >> 4);  // row within the warp's 32 rows
-            const int lv = lane & 15;
-            const uint4 x = ld_shared_v4(stage_smem + lr * kEpiRowBytes + ((lv ^ (lr & 7)) << 4));
-            const int col = col0 + lv * kOutPerVec;
-            if (q * 32 + lr < valid_rows && col < push_cols)
-              st_global_v4(dst_base[d] + static_cast<int64_t>(q * 32 + lr) * dst_ld + col * kOutBytes, x);
-          }
+        for (int itr = 0; itr < 16; ++itr) {
+          const int lr = itr * 2 + (lane >> 4);  // row within the warp's 32 rows
+          const int lv = lane & 15;
+          const uint4 x = ld_shared_v4(stage_smem + lr * kEpiRowBytes + ((lv ^ (lr & 7)) << 4));
+          const int col = col0 + lv * kOutPerVec;
+          if (q * 32 + lr < valid_rows && col < valid_cols)
+            st_global_v4(dst_base + static_cast<int64_t>(q * 32 + lr) * dst_ld + col * kOutBytes, x);
         }
         __syncwarp();
       }
 
-      if (push_partial) {
+      if (fused) {
         __syncwarp();
         if (lane == 0) {
+          bulk_wait_all();          // the bulk copies of this tile have been written
+          fence_proxy_async_all();  // order those async-proxy writes before the flag
           fence_acq_rel_sys();
           st_release_sys(P.flags[t.owner] + P.partial_flag_off +
                              (static_cast<uint32_t>(P.rank) * P.max_owned + slot_idx) * 4 + q,
-                         P.epoch);
-        }
-      } else if (P.mode == kAR && fused) {
-        __syncwarp();
-        if (lane < P.world && lane != P.rank) {
-          fence_acq_rel_sys();
-          st_release_sys(P.flags[lane] + P.result_flag_off + static_cast<uint32_t>(half_lin) * 4 + q,
                          P.epoch);
         }
       }
