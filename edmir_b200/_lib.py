@@ -81,6 +81,8 @@ SIGNATURES = {
     "edm_status_read": (C.c_int, [C.POINTER(C.c_uint32)]),
     "edm_status_clear": (C.c_int, []),
     "edm_set_timeout_ms": (C.c_int, [C.c_uint32]),
+    "edm_profile_enable": (C.c_int, [C.c_int]),
+    "edm_profile_read": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
     "edm_gemm_bf16": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_gemm_fp32_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "edm_gemm_fp32": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
@@ -91,6 +93,7 @@ SIGNATURES = {
     "edm_comm_link_local": (C.c_int, [_vp, C.c_int, _vp]),
     "edm_comm_heap_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp)]),
     "edm_comm_heap_reset": (C.c_int, [_vp]),
+    "edm_comm_p2p_probe": (C.c_int, [_vp, C.c_int, _sz, C.c_int, _vp]),
     "edm_comm_rank": (C.c_int, [_vp]),
     "edm_comm_world": (C.c_int, [_vp]),
     "edm_tp_launch": (C.c_int, [_vp, C.POINTER(TpCall), _vp]),

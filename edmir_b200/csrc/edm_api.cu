@@ -17,6 +17,7 @@ namespace {
 
 thread_local int g_last_cuda_error = 0;
 uint64_t g_timeout_ns = 2000ull * 1000ull * 1000ull;
+int g_profile = 0;
 
 #define EDM_CUDA(expr)                                   \
   do {                                                   \
@@ -250,6 +251,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
+  lp.profile = g_profile;
   return launch_variant(dtype, cg, lp, grid, false, s);
 }
 
@@ -430,6 +432,20 @@ int edm_status_clear(void) {
   EDM_CUDA(cudaMemcpyToSymbol(g_status, z, sizeof(z)));
   return EDM_OK;
 }
+int edm_profile_enable(int on) {
+  g_profile = on ? 1 : 0;
+  return EDM_OK;
+}
+int edm_profile_read(uint64_t out[24], int reset) {
+  if (!out) return EDM_ERR_BAD_ARG;
+  EDM_CUDA(cudaDeviceSynchronize());
+  EDM_CUDA(cudaMemcpyFromSymbol(out, g_prof, sizeof(uint64_t) * 24));
+  if (reset) {
+    uint64_t z[24] = {};
+    EDM_CUDA(cudaMemcpyToSymbol(g_prof, z, sizeof(z)));
+  }
+  return EDM_OK;
+}
 int edm_set_timeout_ms(uint32_t ms) {
   if (ms == 0) return EDM_ERR_BAD_ARG;
   g_timeout_ns = static_cast<uint64_t>(ms) * 1000000ull;
@@ -527,6 +543,25 @@ int edm_comm_heap_reset(edm_comm_t* c) {
 int edm_comm_rank(const edm_comm_t* c) { return c ? c->rank : -1; }
 int edm_comm_world(const edm_comm_t* c) { return c ? c->world : -1; }
 
+int edm_comm_p2p_probe(edm_comm_t* c, int peer, size_t bytes, int mode, void* stream) {
+  if (!c || peer < 0 || peer >= c->world || !c->base[peer] || (mode != 0 && mode != 1)) return EDM_ERR_BAD_ARG;
+  if (bytes == 0 || bytes % 8192 || bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  static bool configured = false;
+  const int smem = 8 * 2 * 8192 + 128;
+  if (!configured) {
+    EDM_CUDA(cudaFuncSetAttribute(p2p_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  // source: first half of the local window; destination: second half of the peer's
+  const char* src = c->base[c->rank] + c->off_window();
+  char* dst = c->base[peer] + c->off_window() + c->window_bytes / 2;
+  p2p_probe_kernel<<<sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(src, dst, bytes, mode);
+  EDM_CUDA(cudaGetLastError());
+  return EDM_OK;
+}
+
 int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   if (!comm || !call) return EDM_ERR_BAD_ARG;
   LaunchParams lp;
@@ -543,6 +578,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
+  lp.profile = g_profile;
   return launch_variant(call->dtype, cg, lp, grid, false, s);
 }
 
@@ -569,6 +605,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   lp.ctas_per_vrank = resident / n / cg * cg;
   if (lp.ctas_per_vrank < cg) return EDM_ERR_CUDA;
   lp.timeout_ns = g_timeout_ns;
+  lp.profile = g_profile;
   return launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
 }
 

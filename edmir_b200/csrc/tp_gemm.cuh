@@ -11,8 +11,12 @@
 //          tile loop consumes shards as their chunk flags arrive (all-gather + GEMM)
 //
 // Both operands are K-major (the reference's "TN" convention, EDM-IR/ir/c-extension/mma.cu:24-25).
-// Roles per CTA (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = peer
-// pushes (AG) / TMEM allocation, warps 4-7 = epilogue (TMEM -> registers -> smem -> global/peer).
+// Roles per CTA (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = peer
+// pushes (AG) or reduction of received partial tiles (RS/AR), warps 4-7 = epilogue (TMEM ->
+// registers -> smem -> global/peer), warp 8 = signaller, warps 9-11 = more reduction (RS/AR).  A system-scope release costs on the
+// order of ten microseconds while remote writes are queued (it drains the SM), so no working
+// warp ever executes one: they post "this data has landed" notes into shared-memory mailboxes
+// and the signaller turns batches of notes into one fence plus relaxed flag stores.
 // Accumulators are double buffered in TMEM (2 x 256 columns) so the epilogue of tile i, which
 // is where the NVLink stores happen, overlaps the MMAs of tile i+1.
 //
@@ -30,7 +34,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockKBytes = 128;  // one 128B swizzle row of K per stage
 constexpr int kPipeBytes = 192 * 1024;  // operand ring: 4 stages of 48 KiB, or 6 of 32 KiB for CTA pairs
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;  // 12 warps, see the role list above (registers are granted per 4 warps)
 constexpr int kMaxRanks = 8;
 constexpr int kMaxVirtualRanks = 4;
 constexpr int kCommWarps = 2;
@@ -56,6 +60,26 @@ enum Status : uint32_t {
 };
 
 __device__ uint32_t g_status[16];
+
+// Optional device-side accounting (LaunchParams::profile): nanoseconds, summed over CTAs, that
+// each role spent waiting or working.  Slot meanings: see ProfSlot.
+enum ProfSlot : int {
+  kProfProducerGatherWait = 0, kProfProducerEmptyWait = 1, kProfMmaFullWait = 2, kProfMmaTmemWait = 3,
+  kProfEpiTmemWait = 4, kProfEpiStagingWait = 5, kProfEpiFlagWait = 6, kProfEpiTotal = 7,
+  kProfReducerFlagWait = 8, kProfReducerTotal = 9, kProfPushLoadWait = 10, kProfPushBufferWait = 11,
+  kProfPushPublish = 12, kProfPushTotal = 13, kProfKernelTotal = 14, kProfCtas = 15,
+  kProfEpiFence = 16, kProfEpiIssue = 17, kProfEpiTmemLoad = 18, kProfPushFence = 19,
+};
+__device__ unsigned long long g_prof[24];
+
+struct ProfTimer {
+  bool on;
+  uint64_t t0;
+  __device__ __forceinline__ explicit ProfTimer(bool enabled) : on(enabled), t0(enabled ? globaltimer_ns() : 0) {}
+  __device__ __forceinline__ void stop(int slot) {
+    if (on) atomicAdd(&g_prof[slot], static_cast<unsigned long long>(globaltimer_ns() - t0));
+  }
+};
 
 struct alignas(64) RankParams {
   CUtensorMap tmap_a[2];  // [0] main A (AG: local gather buffer); [1] 3xTF32 low part / AG local shard
@@ -87,6 +111,8 @@ struct LaunchParams {
   int32_t num_vranks;     // 1 on real multi-GPU runs; >1 = ranks emulated inside one launch
   int32_t ctas_per_vrank;
   uint64_t timeout_ns;
+  int32_t profile;        // 1: accumulate per-role wait times into g_prof
+  int32_t pad;
   RankParams r[kMaxVirtualRanks];
 };
 
@@ -248,6 +274,47 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>((kBlockM * kCG) >> 4) << 24);
 }
 
+template <int V> struct IntTag { static constexpr int value = V; };
+
+// ------------------------------------------------------------------ mailboxes to the signaller
+// One single-producer ring per posting warp: epilogue warps -> 0-3, warps 2-3 -> 4-5, warps 9-11 -> 6-8.
+constexpr int kMailboxes = 9;
+constexpr int kMailboxDepth = 16;
+enum NoteKind : uint64_t {
+  kNoteFlag = 0,     // payload = address of a flag word: store the epoch there
+  kNoteResult = 1,   // payload = result-flag index: store the epoch into every peer's result flag
+  kNoteChunk = 2,    // payload = peer << 24 | chunk: count this warp's share of an all-gather chunk
+};
+struct Mailbox {
+  uint32_t ready;    // notes posted
+  uint32_t done;     // notes published
+  uint32_t closed;   // poster has finished
+  uint32_t pad;
+  uint64_t note[kMailboxDepth];
+};
+__device__ __forceinline__ uint64_t make_note(uint64_t kind, uint64_t payload) { return (kind << 60) | payload; }
+
+// Called by one lane of the posting warp.  Everything the note vouches for must already be
+// complete from this lane's point of view.
+__device__ __forceinline__ void mailbox_post(Mailbox* mb, uint64_t note, uint64_t timeout_ns) {
+  volatile Mailbox* v = mb;
+  const uint32_t r = v->ready;
+  if (r - v->done >= kMailboxDepth) {
+    const uint64_t t0 = globaltimer_ns();
+    while (r - v->done >= kMailboxDepth) {
+      if (aborted() || globaltimer_ns() - t0 > timeout_ns) break;
+      __nanosleep(100);
+    }
+  }
+  v->note[r % kMailboxDepth] = note;
+  __threadfence_block();
+  v->ready = r + 1;
+}
+__device__ __forceinline__ void mailbox_close(Mailbox* mb) {
+  __threadfence_block();
+  reinterpret_cast<volatile Mailbox*>(mb)->closed = 1;
+}
+
 // ------------------------------------------------------------------ output conversion
 template <typename OutT> struct OutPack;
 template <> struct OutPack<__nv_bfloat16> {
@@ -298,8 +365,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[2 * kMaxStages + 4];
+  __shared__ uint64_t bars[2 * kMaxStages + 4 + 2 * kCommWarps];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ Mailbox mbox[kMailboxes];
+  __shared__ uint32_t reduce_next;  // next (half-tile, quarter) unit of the reduction
 
   const int vr = blockIdx.x / lp.ctas_per_vrank;
   const int cta_in_rank = blockIdx.x - vr * lp.ctas_per_vrank;
@@ -309,6 +378,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t pr = kCG == 2 ? cluster_ctarank() : 0u;  // position in the pair; 0 issues the MMAs
   const RankParams& P = lp.r[vr];
   const uint64_t timeout_ns = lp.timeout_ns;
+  const bool prof = lp.profile != 0;
+  ProfTimer prof_kernel(prof && threadIdx.x == 0);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -319,12 +390,22 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_empty = smem_u32(&bars[kStages]);
   const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
+  const uint32_t bar_comm = smem_u32(&bars[2 * kMaxStages + 4]);  // [comm warp][buffer]
+  // all-gather mode gives the last ring stage to the push warps as staging buffers
+  const bool ag_push = P.mode == kAG && P.world > 1;
+  const uint32_t stages = ag_push ? kStages - 1 : kStages;
+  const uint32_t smem_comm = smem_base + (kStages - 1) * kStageBytes;
 
+  if (threadIdx.x == 32) reduce_next = 0;
+  if (threadIdx.x < kMailboxes) {
+    mbox[threadIdx.x].ready = 0; mbox[threadIdx.x].done = 0; mbox[threadIdx.x].closed = 0;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
+    for (int a = 0; a < 2 * kCommWarps; ++a) mbar_init(bar_comm + 8 * a, 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
@@ -351,6 +432,119 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const int num_segs = (num_kb_pass + seg_kb - 1) / seg_kb;
   const int rows_per_rank = P.world > 0 ? P.M / P.world : P.M;
 
+  // ------------------------------------------------------------------ reduction of owned tiles
+  // Adds up the W partial copies of a 128-row half-tile this rank owns (fp32, fixed rank order,
+  // so the result is deterministic) and writes the result to the local output (reduce-scatter)
+  // or to every rank's output (all-reduce).  Work units are (half-tile, row quarter); warps take
+  // them from a shared counter: the two reducer warps from the start, the epilogue warps once
+  // their tiles are done.  None of this holds up the MMA pipeline.
+  const bool fused_reduce = (P.mode == kRS || P.mode == kAR) && P.world > 1;
+  auto reduce_units = [&](Mailbox* note_box, bool rprof) {
+    const int W = P.world;
+    const int n_items = walk.owned_count(P.rank) * kCG;  // half-tiles owned by this rank
+    const int my_items = n_items > cta_in_rank ? (n_items - cta_in_rank + lp.ctas_per_vrank - 1) / lp.ctas_per_vrank : 0;
+    while (true) {
+      uint32_t u = 0;
+      if (lane == 0) u = atomicAdd(&reduce_next, 1u);
+      u = __shfl_sync(0xffffffffu, u, 0);
+      if (u >= static_cast<uint32_t>(my_items) * 4u) break;
+      const int item = cta_in_rank + static_cast<int>(u >> 2) * lp.ctas_per_vrank;
+      const int qq = static_cast<int>(u & 3u);
+      const int idx = item / kCG, hp = item - idx * kCG;  // owned tile, half within the pair tile
+      int m_blk, n_blk;
+      walk.owned_tile(P.rank, idx, m_blk, n_blk);
+      const int m0 = (m_blk * kCG + hp) * kBlockM, n0 = n_blk * kBlockN;
+      const int valid_rows = min(kBlockM, P.M - m0), valid_cols = min(kBlockN, P.N - n0);
+      const int64_t out_row0 = P.mode == kRS ? m0 - P.rank * rows_per_rank : m0;
+      const int64_t ld_bytes = P.ld_out * kOutBytes;
+      const char* slot0 = P.win[P.rank] + static_cast<int64_t>(item) * kTileOutBytes;
+      const int64_t src_stride = static_cast<int64_t>(P.max_owned) * kTileOutBytes;
+      {
+        ProfTimer rf(rprof);
+        if (lane < W)
+          wait_flag(P.flags[P.rank] + P.partial_flag_off +
+                        (static_cast<uint32_t>(lane) * P.max_owned + item) * 4 + qq,
+                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | item);
+        __syncwarp();
+        rf.stop(kProfReducerFlagWait);
+#pragma unroll 1
+        for (int h = 0; h < kPasses; ++h) {
+          const char* blk = slot0 + (h * 4 + qq) * kEpiWarpBytes;  // 512 vectors of 16 B
+          // kW sources x kU vectors per lane are loaded before any is used (12 to 20 loads of
+          // 16 B in flight per lane whatever the group size), then summed in rank order
+          auto run = [&](auto wtag) {
+            constexpr int kW = decltype(wtag)::value;
+            constexpr int kVecs = kEpiWarpBytes / 16 / 32;  // 16 vectors per lane per block
+            constexpr int kU = kW == 2 ? 8 : (kW <= 5 ? 4 : 2);  // divides kVecs; 12 to 20 loads in flight
+#pragma unroll 1
+            for (int it = 0; it < kVecs; it += kU) {
+              uint4 x[kU][kW];
+#pragma unroll
+              for (int u = 0; u < kU; ++u)
+#pragma unroll
+                for (int src = 0; src < kW; ++src)
+                  x[u][src] = ld_cg_v4(blk + src * src_stride + ((it + u) * 32 + lane) * 16);
+#pragma unroll
+              for (int u = 0; u < kU; ++u) {
+                float sum[kOutPerVec];
+#pragma unroll
+                for (int e = 0; e < kOutPerVec; ++e) sum[e] = 0.f;
+#pragma unroll
+                for (int src = 0; src < kW; ++src) {
+                  if constexpr (kOutBytes == 2) {
+                    OutPack<__nv_bfloat16>::add16B(sum, x[u][src]);
+                  } else {
+                    sum[0] += __uint_as_float(x[u][src].x); sum[1] += __uint_as_float(x[u][src].y);
+                    sum[2] += __uint_as_float(x[u][src].z); sum[3] += __uint_as_float(x[u][src].w);
+                  }
+                }
+                uint4 o;
+                if constexpr (kOutBytes == 2) {
+                  o = OutPack<__nv_bfloat16>::pack8(sum);
+                } else {
+                  o.x = __float_as_uint(sum[0]); o.y = __float_as_uint(sum[1]);
+                  o.z = __float_as_uint(sum[2]); o.w = __float_as_uint(sum[3]);
+                }
+                // undo the staging layout: vector -> (row, logical 16B vector)
+                const int vec = (it + u) * 32 + lane;
+                const int r = vec >> 4, lv = (vec & 15) ^ (r & 7);
+                const int trow = qq * 32 + r, col = h * kColsPerPass + lv * kOutPerVec;
+                if (trow < valid_rows && col < valid_cols) {
+                  const int64_t off = (out_row0 + trow) * ld_bytes + static_cast<int64_t>(n0 + col) * kOutBytes;
+                  if (P.mode == kRS) {
+                    st_global_v4(static_cast<char*>(P.out) + off, o);
+                  } else {
+#pragma unroll
+                    for (int d = 0; d < kW; ++d)
+                      st_global_v4(static_cast<char*>(P.peer_out[(P.rank + d) % kW]) + off, o);
+                  }
+                }
+              }
+            }
+          };
+          switch (W) {
+            case 2: run(IntTag<2>{}); break;
+            case 3: run(IntTag<3>{}); break;
+            case 4: run(IntTag<4>{}); break;
+            case 5: run(IntTag<5>{}); break;
+            case 6: run(IntTag<6>{}); break;
+            case 7: run(IntTag<7>{}); break;
+            default: run(IntTag<8>{}); break;
+          }
+        }
+        if (P.mode == kAR) {
+          // this quarter of the reduced half-tile has been stored to every rank's output
+          __syncwarp();
+          if (lane == 0) {
+            const int lin = idx * W + P.rank;
+            mailbox_post(&*note_box, make_note(kNoteResult, static_cast<uint32_t>(lin * kCG + hp) * 4 + qq),
+                         timeout_ns);
+          }
+        }
+      }
+    }
+  };
+
   if (warp == 0) {
     // ============================ TMA producer ============================
     if (lane == 0) {
@@ -373,6 +567,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             amap = &P.tmap_a[1];
             a_row = m0 - P.rank * rows_per_rank;
           } else {
+            ProfTimer pt(prof);
             for (int s = s_lo; s <= s_hi; ++s) {
               const int lo = max(m0, s * rows_per_rank) - s * rows_per_rank;
               const int hi = min(m1, (s + 1) * rows_per_rank) - s * rows_per_rank;
@@ -381,6 +576,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                           timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
             }
             fence_proxy_async_all();  // peer-written rows are read by the async proxy next
+            pt.stop(kProfProducerGatherWait);
           }
         }
         for (int seg = 0; seg < num_segs; ++seg) {
@@ -390,8 +586,12 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
             const CUtensorMap* bm = (P.passes == 3 && pass == 1) ? &P.tmap_b[1] : &P.tmap_b[0];
             for (int j = j0; j < j1; ++j, ++it) {
-              const uint32_t s = it % kStages;
-              wait_mbar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
+              const uint32_t s = it % stages;
+              {
+                ProfTimer pt(prof);
+                wait_mbar(bar_empty + 8 * s, ((it / stages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
+                pt.stop(kProfProducerEmptyWait);
+              }
               const uint32_t sa = smem_base + s * kStageBytes;
               if constexpr (kCG == 1) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
@@ -418,13 +618,21 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         if (!walk.at(i).valid) continue;
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
           const uint32_t acc = unit & 1u;
-          wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit);
+          {
+            ProfTimer pt(prof);
+            wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit);
+            pt.stop(kProfMmaTmemWait);
+          }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kBlockN;
           const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
           for (int kb = 0; kb < nkb; ++kb, ++it) {
-            const uint32_t s = it % kStages;
-            wait_mbar(bar_full + 8 * s, (it / kStages) & 1u, timeout_ns, kTimeoutFullBar, it);
+            const uint32_t s = it % stages;
+            {
+              ProfTimer pt(prof);
+              wait_mbar(bar_full + 8 * s, (it / stages) & 1u, timeout_ns, kTimeoutFullBar, it);
+              pt.stop(kProfMmaFullWait);
+            }
             tc_fence_after();
             const uint32_t sa = smem_base + s * kStageBytes;
             const uint64_t adesc = make_smem_desc(sa);
@@ -445,159 +653,130 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
   } else if (warp < 2 + kCommWarps) {
     // ============================ all-gather pushes ============================
-    if (P.mode == kAG && P.world > 1) {
+    if (ag_push) {
+      // Each push warp moves 8 KiB pieces of the local shard: bulk load into a shared-memory
+      // buffer, bulk store into the peer's gather buffer.  Both are asynchronous; the lane only
+      // blocks on the (local, short) load, so stores stay in flight back to back.  A chunk is
+      // published to its peer once the stores of it are known complete, which is checked one
+      // chunk late (wait for all but the newest groups) so the link never drains for a flag.
       const int cw = warp - 2;
-      const int gw = cta_in_rank * kCommWarps + cw;
-      const int total_warps = lp.ctas_per_vrank * kCommWarps;
-      const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
-      const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
-      const int first_d = P.ag_local_direct ? 1 : 0;
-      // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after its
-      // own), then to rank-2, ...; every GPU sends to and receives from one peer at a time
-      for (int d = first_d; d < P.world; ++d) {
-        const int peer = (P.rank - d + P.world) % P.world;
-        const char* src = static_cast<const char*>(P.x_local);
-        char* dst = static_cast<char*>(P.gather[peer]);
+      {
+        constexpr uint32_t kPiece = 8192;
+        const int gw = cta_in_rank * kCommWarps + cw;
+        const int total_warps = lp.ctas_per_vrank * kCommWarps;
+        const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
+        const int64_t row_bytes = static_cast<int64_t>(P.K) * kElemBytes;
         const int64_t src_ld = P.ld_x * kElemBytes;
-        const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
-        const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
-        for (int c = 0; c < P.ag_chunks; ++c) {
-          const int r_lo = c * chunk_rows;
-          const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
-          const int64_t nvec = static_cast<int64_t>(max(r_hi - r_lo, 0)) * row_vecs;
-          constexpr int kUnroll = 8;
-          for (int64_t v0 = static_cast<int64_t>(gw) * 32 * kUnroll; v0 < nvec;
-               v0 += static_cast<int64_t>(total_warps) * 32 * kUnroll) {
-            uint4 buf[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-              const int64_t v = v0 + u * 32 + lane;
-              if (v < nvec) {
-                const int64_t row = v / row_vecs, col = v - row * row_vecs;
-                buf[u] = ld_cg_v4(src + (r_lo + row) * src_ld + col * 16);
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-              const int64_t v = v0 + u * 32 + lane;
-              if (v < nvec) {
-                const int64_t row = v / row_vecs, col = v - row * row_vecs;
-                st_global_v4(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, buf[u]);
-              }
-            }
-          }
-          __syncwarp();
-          if (lane == 0) {
-            // last arriving warp of this GPU publishes the chunk to the peer
-            fence_acq_rel_sys();
-            uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
-            const uint32_t prev = atomicAdd(ctr, 1u);
-            if (prev == static_cast<uint32_t>(total_warps - 1)) {
-              *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;
-              fence_acq_rel_sys();
-              st_release_sys(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, P.epoch);
-            }
-          }
-        }
-      }
-    }
-    if ((P.mode == kRS || P.mode == kAR) && P.world > 1) {
-      // ============================ reducer ============================
-      // Adds up the W partial copies of every 128-row half-tile this rank owns (fp32, fixed rank
-      // order, so the result is deterministic) and writes the result: to the local output
-      // (reduce-scatter) or to every rank's output (all-reduce).  It runs beside the tile loop and
-      // never holds up the MMA pipeline; each of the two warps takes two of the four row quarters.
-      const int cw = warp - 2;
-      const int W = P.world;
-      const int n_items = walk.owned_count(P.rank) * kCG;  // half-tiles owned by this rank
-      constexpr int kU = 4;                                 // 16B vectors per lane in flight, per source
-      for (int item = cta_in_rank; item < n_items; item += lp.ctas_per_vrank) {
-        const int idx = item / kCG, hp = item - idx * kCG;  // owned tile, half within the pair tile
-        int m_blk, n_blk;
-        walk.owned_tile(P.rank, idx, m_blk, n_blk);
-        const int m0 = (m_blk * kCG + hp) * kBlockM, n0 = n_blk * kBlockN;
-        const int valid_rows = min(kBlockM, P.M - m0), valid_cols = min(kBlockN, P.N - n0);
-        const int64_t out_row0 = P.mode == kRS ? m0 - P.rank * rows_per_rank : m0;
-        const int64_t ld_bytes = P.ld_out * kOutBytes;
-        const char* slot0 = P.win[P.rank] + static_cast<int64_t>(item) * kTileOutBytes;
-        const int64_t src_stride = static_cast<int64_t>(P.max_owned) * kTileOutBytes;
-        for (int qq = 2 * cw; qq < 2 * cw + 2; ++qq) {
-          if (lane < W)
-            wait_flag(P.flags[P.rank] + P.partial_flag_off +
-                          (static_cast<uint32_t>(lane) * P.max_owned + item) * 4 + qq,
-                      P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | item);
-          __syncwarp();
-#pragma unroll 1
-          for (int h = 0; h < kPasses; ++h) {
-            const char* blk = slot0 + (h * 4 + qq) * kEpiWarpBytes;  // 512 vectors of 16 B
-#pragma unroll 1
-            for (int it = 0; it < kEpiWarpBytes / 16 / 32; it += kU) {
-              uint4 x[kU][kMaxRanks];
-#pragma unroll
-              for (int u = 0; u < kU; ++u)
-#pragma unroll
-                for (int src = 0; src < kMaxRanks; ++src)
-                  if (src < W) x[u][src] = ld_cg_v4(blk + src * src_stride + ((it + u) * 32 + lane) * 16);
-#pragma unroll
-              for (int u = 0; u < kU; ++u) {
-                float sum[kOutPerVec];
-#pragma unroll
-                for (int e = 0; e < kOutPerVec; ++e) sum[e] = 0.f;
-#pragma unroll
-                for (int src = 0; src < kMaxRanks; ++src) {
-                  if (src < W) {
-                    if constexpr (kOutBytes == 2) {
-                      OutPack<__nv_bfloat16>::add16B(sum, x[u][src]);
-                    } else {
-                      sum[0] += __uint_as_float(x[u][src].x); sum[1] += __uint_as_float(x[u][src].y);
-                      sum[2] += __uint_as_float(x[u][src].z); sum[3] += __uint_as_float(x[u][src].w);
-                    }
-                  }
-                }
-                uint4 o;
-                if constexpr (kOutBytes == 2) {
-                  o = OutPack<__nv_bfloat16>::pack8(sum);
+        const bool flat = (src_ld == row_bytes);  // shard is one contiguous byte range
+        const int first_d = P.ag_local_direct ? 1 : 0;
+        const uint32_t buf0 = smem_comm + cw * 2 * kPiece;
+        const uint32_t bar0 = bar_comm + cw * 16;
+        uint32_t cnt = 0;             // pieces issued by lane 0
+        const bool pprof = prof && lane == 0;
+        ProfTimer push_total(pprof);
+
+        // Lane 0 owns the bulk copies.  Chunks are numbered in issue order (seq = peer slot *
+        // chunks + chunk).  A finished chunk is handed to the signaller once its stores are known
+        // to be written; that check is made kLagPieces pieces later, when it no longer has to
+        // wait ("all but the kLagPieces newest copy groups are complete").
+        constexpr int kLagPieces = 6;
+        constexpr int kQueue = 8;
+        uint32_t fin_cnt[kQueue];     // value of cnt when chunk (seq % kQueue) was finished
+        int seq_posted = 0, seq_finished = 0;
+        auto post_chunk = [&](int seq) {
+          const int d = first_d + seq / P.ag_chunks, c = seq - (seq / P.ag_chunks) * P.ag_chunks;
+          const int peer = (P.rank - d + P.world) % P.world;
+          mailbox_post(&mbox[4 + cw], make_note(kNoteChunk, (static_cast<uint64_t>(peer) << 24) | c), timeout_ns);
+        };
+        auto settle_all = [&]() {
+          ProfTimer pt(pprof);
+          bulk_wait_pending<0>();
+          fence_proxy_async_all();
+          for (; seq_posted < seq_finished; ++seq_posted) post_chunk(seq_posted);
+          pt.stop(kProfPushPublish);
+        };
+
+        // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after
+        // its own), then to rank-2, ...: every GPU sends to and receives from one peer at a time
+        for (int d = first_d; d < P.world; ++d) {
+          const int peer = (P.rank - d + P.world) % P.world;
+          const char* src = static_cast<const char*>(P.x_local);
+          char* dst = static_cast<char*>(P.gather[peer]) + static_cast<int64_t>(P.rank) * rows_per_rank * row_bytes;
+          for (int c = 0; c < P.ag_chunks; ++c) {
+            const int r_lo = c * chunk_rows;
+            const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
+            const int64_t rows = max(r_hi - r_lo, 0);
+            // pieces: flat -> 8 KiB slices of the chunk; strided -> slices of each row
+            const int64_t per_row = (row_bytes + kPiece - 1) / kPiece;
+            const int64_t npieces = flat ? (rows * row_bytes + kPiece - 1) / kPiece : rows * per_row;
+            for (int64_t k = gw; k < npieces; k += total_warps) {
+              if (lane == 0) {
+                int64_t s_off, d_off;
+                uint32_t len;
+                if (flat) {
+                  s_off = d_off = r_lo * row_bytes + k * kPiece;
+                  len = static_cast<uint32_t>(min(static_cast<int64_t>(kPiece), rows * row_bytes - k * kPiece));
                 } else {
-                  o.x = __float_as_uint(sum[0]); o.y = __float_as_uint(sum[1]);
-                  o.z = __float_as_uint(sum[2]); o.w = __float_as_uint(sum[3]);
+                  const int64_t r = k / per_row, part = k - r * per_row;
+                  s_off = (r_lo + r) * src_ld + part * kPiece;
+                  d_off = (r_lo + r) * row_bytes + part * kPiece;
+                  len = static_cast<uint32_t>(min(static_cast<int64_t>(kPiece), row_bytes - part * kPiece));
                 }
-                // undo the staging layout: vector -> (row, logical 16B vector)
-                const int vec = (it + u) * 32 + lane;
-                const int r = vec >> 4, lv = (vec & 15) ^ (r & 7);
-                const int trow = qq * 32 + r, col = h * kColsPerPass + lv * kOutPerVec;
-                if (trow < valid_rows && col < valid_cols) {
-                  const int64_t off = (out_row0 + trow) * ld_bytes + static_cast<int64_t>(n0 + col) * kOutBytes;
-                  if (P.mode == kRS) {
-                    st_global_v4(static_cast<char*>(P.out) + off, o);
-                  } else {
-#pragma unroll
-                    for (int d = 0; d < kMaxRanks; ++d)
-                      if (d < W) st_global_v4(static_cast<char*>(P.peer_out[(P.rank + d) % W]) + off, o);
-                  }
-                }
+                const uint32_t b = cnt & 1u;
+                ProfTimer pb(pprof);
+                bulk_wait_read_pending<1>();  // the store that last used this buffer has read it
+                pb.stop(kProfPushBufferWait);
+                mbar_arrive_expect_tx(bar0 + 8 * b, len);
+                bulk_load(buf0 + b * kPiece, src + s_off, len, bar0 + 8 * b);
+                ProfTimer pl(pprof);
+                wait_mbar(bar0 + 8 * b, (cnt >> 1) & 1u, timeout_ns, kTimeoutFullBar, 0x80000000u | cnt);
+                pl.stop(kProfPushLoadWait);
+                bulk_store(dst + d_off, buf0 + b * kPiece, len);
+                bulk_commit();
+              }
+              ++cnt;
+              if (lane == 0 && seq_posted < seq_finished &&
+                  cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces)) {
+                ProfTimer pt(pprof);
+                bulk_wait_pending<kLagPieces>();
+                fence_proxy_async_all();
+                while (seq_posted < seq_finished &&
+                       cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces))
+                  post_chunk(seq_posted++);
+                pt.stop(kProfPushPublish);
               }
             }
-          }
-          if (P.mode == kAR) {
-            // this quarter of the reduced half-tile now sits in every rank's output
-            __syncwarp();
-            if (lane < W && lane != P.rank) {
-              fence_acq_rel_sys();
-              const int lin = idx * W + P.rank;
-              st_release_sys(P.flags[lane] + P.result_flag_off +
-                                 static_cast<uint32_t>(lin * kCG + hp) * 4 + qq, P.epoch);
+            if (lane == 0) {
+              if (seq_finished - seq_posted == kQueue) settle_all();  // queue full
+              fin_cnt[seq_finished % kQueue] = cnt;
+              ++seq_finished;
             }
           }
         }
+        if (lane == 0) settle_all();
+        push_total.stop(kProfPushTotal);
       }
     }
-  } else {
+    if (fused_reduce) {
+      // ============================ reducer ============================
+      const bool rprof = prof && lane == 0 && warp == 2;
+      ProfTimer red_total(rprof);
+      reduce_units(&mbox[4 + (warp - 2)], rprof);
+      red_total.stop(kProfReducerTotal);
+    }
+    __syncwarp();
+    if (lane == 0) mailbox_close(&mbox[4 + (warp - 2)]);
+  } else if (warp < 8) {
     // ============================ epilogue ============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool eprof = prof && lane == 0 && q == 0;
+    ProfTimer epi_total(eprof);
     const uint32_t stage_smem = smem_epi + q * kEpiWarpBytes;
     const int row = q * 32 + lane;  // row within the tile owned by this thread
     uint32_t unit = 0;  // (tile, K segment) counter, in step with the MMA warp
     bool bulk_pending = false;  // a bulk copy out of this warp's staging rows may still be reading them
+    uint32_t* pend_old = nullptr;  // flags of the (up to two) shipped tiles whose copies may be in flight
+    uint32_t* pend_new = nullptr;
     const bool fused = (P.mode == kRS || P.mode == kAR) && P.world > 1;
     // running fp32 sums of this thread's row: [chunk][row][32 floats], private to the CTA
     float* my_scratch = P.scratch == nullptr ? nullptr
@@ -641,8 +820,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       }
       const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
-      if (lane == 0)
+      if (lane == 0) {
+        ProfTimer pt(eprof);
         wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter);
+        pt.stop(kProfEpiTmemWait);
+      }
       __syncwarp();
       tc_fence_after();
 
@@ -666,8 +848,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         for (int j = 0; j < kChunksPerPass; ++j) {
           const int c = h * kChunksPerPass + j;  // 32-column chunk of the tile
           uint32_t raw[32];
+          ProfTimer ptl(eprof);
           tmem_ld_32x32(taddr + c * 32, raw);
           tmem_ld_wait();
+          ptl.stop(kProfEpiTmemLoad);
           if (c == kBlockN / 32 - 1) {
             // accumulator fully read: hand the TMEM buffer back to the MMA warp
             tc_fence_before();
@@ -695,7 +879,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           }
           if (j == 0 && bulk_pending) {
             // the previous pass's bulk copy may still be reading the staging rows
-            if (lane == 0) bulk_wait_read_all();
+            if (lane == 0) {
+              ProfTimer pt(eprof);
+              bulk_wait_read_all();
+              pt.stop(kProfEpiStagingWait);
+            }
             __syncwarp();
             bulk_pending = false;
           }
@@ -719,8 +907,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
+            ProfTimer pi(eprof);
             bulk_store(dst_base + (h * 4 + q) * kEpiWarpBytes, stage_smem, kEpiWarpBytes);
             bulk_commit();
+            pi.stop(kProfEpiIssue);
           }
           bulk_pending = true;
           continue;
@@ -740,18 +930,37 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         __syncwarp();
       }
 
-      if (fused) {
-        __syncwarp();
-        if (lane == 0) {
-          bulk_wait_all();          // the bulk copies of this tile have been written
-          fence_proxy_async_all();  // order those async-proxy writes before the flag
-          fence_acq_rel_sys();
-          st_release_sys(P.flags[t.owner] + P.partial_flag_off +
-                             (static_cast<uint32_t>(P.rank) * P.max_owned + slot_idx) * 4 + q,
-                         P.epoch);
+      if (fused && lane == 0) {
+        // Two shipped tiles may be in flight per warp.  When a third has been issued, the oldest
+        // is certainly older than the 2 * kPasses newest copy groups, so waiting for "all but
+        // those" settles it without draining the link; then the signaller gets its flag.
+        if (pend_old != nullptr) {
+          ProfTimer pt(eprof);
+          bulk_wait_pending<2 * kPasses>();
+          fence_proxy_async_all();
+          pt.stop(kProfEpiFlagWait);
+          mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
         }
+        pend_old = pend_new;
+        pend_new = P.flags[t.owner] + P.partial_flag_off +
+                   (static_cast<uint32_t>(P.rank) * P.max_owned + slot_idx) * 4 + q;
       }
     }
+    if (lane == 0) {
+      if (pend_new != nullptr) {
+        bulk_wait_pending<0>();
+        fence_proxy_async_all();
+        if (pend_old != nullptr)
+          mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
+        mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_new)), timeout_ns);
+      }
+    }
+    __syncwarp();
+    if (fused_reduce) reduce_units(&mbox[q], false);  // tiles done: help add up the owned tiles
+    __syncwarp();
+    if (lane == 0) mailbox_close(&mbox[q]);
+    __syncwarp();
+    epi_total.stop(kProfEpiTotal);
 
     if (P.mode == kAR && fused) {
       // the call is complete on this rank only when every other owner's tiles have arrived
@@ -767,9 +976,65 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
   }
 
+  else if (warp == 8) {
+    // ============================ signaller ============================
+    // Lane w serves mailbox w.  A batch of notes costs one system-scope fence; the flag stores
+    // after it are relaxed (the fence already orders the landed data before them).
+    if (lane < kMailboxes) {
+      volatile Mailbox* mb = &mbox[lane];
+      uint32_t done = 0;
+      uint64_t idle_since = 0;
+      const int total_push_warps = lp.ctas_per_vrank * kCommWarps;
+      while (true) {
+        const uint32_t ready = mb->ready;
+        if (ready != done) {
+          __threadfence_block();
+          fence_acq_rel_sys();
+          for (; done != ready; ++done) {
+            const uint64_t note = mb->note[done % kMailboxDepth];
+            const uint64_t kind = note >> 60, payload = note & ((1ull << 60) - 1);
+            if (kind == kNoteFlag) {
+              st_relaxed_sys(reinterpret_cast<uint32_t*>(payload), P.epoch);
+            } else if (kind == kNoteResult) {
+              for (int peer = 0; peer < P.world; ++peer)
+                if (peer != P.rank)
+                  st_relaxed_sys(P.flags[peer] + P.result_flag_off + static_cast<uint32_t>(payload), P.epoch);
+            } else {
+              const int peer = static_cast<int>(payload >> 24), c = static_cast<int>(payload & 0xFFFFFF);
+              uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
+              if (atomicAdd(ctr, 1u) == static_cast<uint32_t>(total_push_warps - 1)) {
+                // last push warp of this GPU: every piece of the chunk has been written
+                *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;
+                fence_acq_rel_sys();
+                st_relaxed_sys(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, P.epoch);
+              }
+            }
+          }
+          mb->done = done;
+          idle_since = 0;
+        } else if (mb->closed) {
+          if (mb->ready == done) break;
+        } else {
+          __nanosleep(200);
+          if (aborted()) break;
+          const uint64_t now = globaltimer_ns();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > 4 * timeout_ns) break;  // posters are bounded; this is a backstop
+        }
+      }
+    }
+  } else {
+    // ============================ extra reducers (warps 9-11) ============================
+    if (fused_reduce) reduce_units(&mbox[6 + (warp - 9)], false);
+    __syncwarp();
+    if (lane == 0) mailbox_close(&mbox[6 + (warp - 9)]);
+  }
+
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  prof_kernel.stop(kProfKernelTotal);
+  if (prof && threadIdx.x == 0) atomicAdd(&g_prof[kProfCtas], 1ull);
   if (aborted()) __nanosleep(200000);  // let loads that are still in flight land before smem goes away
   // a pair leaves together: the partner may still signal this CTA's barriers or read its smem
   if constexpr (kCG == 2) cluster_sync_all();
@@ -793,6 +1058,58 @@ __global__ void split_tf32_kernel(const float* __restrict__ x, float* __restrict
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rem));
     hi[i] = __uint_as_float(h);
     lo[i] = __uint_as_float(l);
+  }
+}
+
+// ------------------------------------------------------------------ link probe
+// Copies `bytes` from local memory into a peer's window, with the two store mechanisms the
+// fused kernel uses, so the host can measure what the link sustains (calibration of the
+// schedule selector's transfer term).  mode 0: 16-byte loads and stores from every thread;
+// mode 1: every warp stages 8 KiB in shared memory and ships it with one bulk copy.
+__global__ void __launch_bounds__(256, 1)
+p2p_probe_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t bytes, int mode) {
+  extern __shared__ uint8_t probe_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (mode == 0) {
+    const size_t nvec = bytes / 16;
+    constexpr int kU = 8;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * kU;
+    for (size_t v0 = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x - lane) * kU; v0 < nvec; v0 += stride) {
+      uint4 buf[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const size_t v = v0 + u * 32 + lane;
+        if (v < nvec) buf[u] = ld_cg_v4(src + v * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const size_t v = v0 + u * 32 + lane;
+        if (v < nvec) st_global_v4(dst + v * 16, buf[u]);
+      }
+    }
+  } else {
+    constexpr uint32_t kChunk = 8192;
+    const uint32_t base = (smem_u32(probe_smem) + 127u) & ~127u;
+    const uint32_t buf0 = base + warp * 2 * kChunk;
+    const size_t nchunks = bytes / kChunk;
+    const size_t gw = static_cast<size_t>(blockIdx.x) * 8 + warp, tw = static_cast<size_t>(gridDim.x) * 8;
+    int b = 0;
+    for (size_t c = gw; c < nchunks; c += tw, b ^= 1) {
+      const uint32_t sb = buf0 + b * kChunk;
+      // the bulk copy issued two iterations ago out of this buffer must have read it
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        st_shared_v4(sb + (u * 32 + lane) * 16, ld_cg_v4(src + c * kChunk + (u * 32 + lane) * 16));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        bulk_store(dst + c * kChunk, sb, kChunk);
+        bulk_commit();
+      }
+    }
+    if (lane == 0) bulk_wait_all();
   }
 }
 

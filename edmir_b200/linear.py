@@ -117,3 +117,22 @@ def clear_status() -> None:
 
 def set_timeout_ms(ms: int) -> None:
     _lib.check(_lib.load().edm_set_timeout_ms(int(ms)), "edm_set_timeout_ms")
+
+
+PROFILE_SLOTS = ("producer_gather_wait", "producer_stage_wait", "mma_operand_wait", "mma_accumulator_wait",
+                 "epilogue_accumulator_wait", "epilogue_staging_wait", "epilogue_landing_wait", "epilogue_total",
+                 "reducer_partial_wait", "reducer_total", "push_load_wait", "push_buffer_wait", "push_publish",
+                 "push_total", "kernel_total", "ctas", "epilogue_flag_fence", "epilogue_copy_issue",
+                 "epilogue_accumulator_load", "push_flag_fence", "r20", "r21", "r22", "r23")
+
+
+def profile_enable(on: bool = True) -> None:
+    """Switch the device-side per-role time accounting on or off for later launches."""
+    _lib.check(_lib.load().edm_profile_enable(1 if on else 0), "edm_profile_enable")
+
+
+def profile_read(reset: bool = True) -> dict:
+    """Accumulated nanoseconds per role (summed over CTAs) since the last reset, by name."""
+    buf = (C.c_uint64 * 24)()
+    _lib.check(_lib.load().edm_profile_read(buf, 1 if reset else 0), "edm_profile_read")
+    return dict(zip(PROFILE_SLOTS, (int(v) for v in buf)))

@@ -98,6 +98,10 @@ class SymmetricContext:
     def reset_heap(self) -> None:
         _lib.check(self._lib.edm_comm_heap_reset(self._h), "edm_comm_heap_reset")
 
+    def p2p_probe(self, peer: int, nbytes: int, mode: int = 0) -> None:
+        """Launch one link-probe copy of ``nbytes`` into ``peer``'s window (time it with events)."""
+        _lib.check(self._lib.edm_comm_p2p_probe(self._h, peer, nbytes, mode, _stream()), "edm_comm_p2p_probe")
+
     # ---------------------------------------------------------------- launches
     def _call(self, op: str, a, b, out, chunks: int = 1) -> "_lib.TpCall":
         _require_cuda(a, b, out)

@@ -54,6 +54,20 @@ int edm_last_cuda_error(void);
 int edm_status_read(uint32_t out[16]);
 int edm_status_clear(void);
 
+/* Device-side accounting for tracing (the reference times phases with CUDA events only,
+ * EDM-IR/ir/trace.py:38-43; this looks inside a launch).  While enabled, every launch adds the
+ * nanoseconds each role spent waiting or working, summed over CTAs, to 24 counters:
+ * 0 producer waiting for gathered shards, 1 producer waiting for a free stage, 2 MMA waiting for
+ * operands, 3 MMA waiting for an accumulator, 4 epilogue waiting for an accumulator, 5 epilogue
+ * waiting to reuse staging, 6 epilogue waiting for pushed tiles to land, 7 epilogue total,
+ * 8 reducer waiting for partial tiles, 9 reducer total, 10 push warps waiting for local loads,
+ * 11 push warps waiting for a buffer, 12 push warps publishing chunks, 13 push warps total,
+ * 14 kernel total, 15 number of CTAs counted, 16 epilogue flag fences, 17 epilogue copy issue,
+ * 18 epilogue accumulator loads, 19 push-warp flag fences, 20-23 reserved.
+ * edm_profile_read synchronises the device. */
+int edm_profile_enable(int on);
+int edm_profile_read(uint64_t out[24], int reset);
+
 /* Upper bound for every device-side wait, in milliseconds (default 2000). */
 int edm_set_timeout_ms(uint32_t ms);
 
@@ -88,6 +102,12 @@ int edm_comm_link_local(edm_comm_t* comm, int peer, edm_comm_t* peer_comm);
 /* Bump allocation from the symmetric heap; every rank must make the same sequence of calls. */
 int edm_comm_heap_alloc(edm_comm_t* comm, size_t bytes, void** out);
 int edm_comm_heap_reset(edm_comm_t* comm);
+/* Link probe for calibration: copies `bytes` (a multiple of 8192, at most half the window) from
+ * this rank's window into `peer`'s with mode 0 = 16-byte stores from every thread, mode 1 =
+ * 8 KiB bulk copies staged through shared memory.  The caller times it with CUDA events; the
+ * figures feed the selector's transfer term ("calibrated from ... P2P tests",
+ * paper/mlsys-2027/model.md:111).  Both ranks of a pair may probe each other at once. */
+int edm_comm_p2p_probe(edm_comm_t* comm, int peer, size_t bytes, int mode, void* stream);
 int edm_comm_rank(const edm_comm_t* comm);
 int edm_comm_world(const edm_comm_t* comm);
 
