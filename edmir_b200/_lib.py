@@ -110,7 +110,8 @@ _lib = None
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    # EDM_LIB_PATH selects another build of the same library (kernel experiments)
+    return os.environ.get("EDM_LIB_PATH") or _build.LIB_PATH
 
 
 def load() -> C.CDLL:

@@ -252,6 +252,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
+  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   return launch_variant(dtype, cg, lp, grid, false, s);
 }
 
@@ -579,6 +580,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
+  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   return launch_variant(call->dtype, cg, lp, grid, false, s);
 }
 
@@ -606,6 +608,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   if (lp.ctas_per_vrank < cg) return EDM_ERR_CUDA;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
+  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   return launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
 }
 

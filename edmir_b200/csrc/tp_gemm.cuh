@@ -112,7 +112,7 @@ struct LaunchParams {
   int32_t ctas_per_vrank;
   uint64_t timeout_ns;
   int32_t profile;        // 1: accumulate per-role wait times into g_prof
-  int32_t pad;
+  int32_t stage_limit;    // experiments: use at most this many ring stages (0 = all)
   RankParams r[kMaxVirtualRanks];
 };
 
@@ -393,7 +393,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_comm = smem_u32(&bars[2 * kMaxStages + 4]);  // [comm warp][buffer]
   // all-gather mode gives the last ring stage to the push warps as staging buffers
   const bool ag_push = P.mode == kAG && P.world > 1;
-  const uint32_t stages = ag_push ? kStages - 1 : kStages;
+  uint32_t stages = ag_push ? kStages - 1 : kStages;
+  if (lp.stage_limit > 0 && static_cast<uint32_t>(lp.stage_limit) < stages) stages = lp.stage_limit;
   const uint32_t smem_comm = smem_base + (kStages - 1) * kStageBytes;
 
   if (threadIdx.x == 32) reduce_next = 0;
@@ -550,7 +551,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     if (lane == 0) {
       tma_prefetch_desc(&P.tmap_a[0]);
       tma_prefetch_desc(&P.tmap_b[0]);
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;  // ring position: stage and the phase bit of its current use
       for (int i = cta; i < walk.positions; i += num_ctas) {
         const Tile t = walk.at(i);
         if (!t.valid) continue;
@@ -585,11 +586,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             // split fp32: (lo,hi), (hi,lo), then (hi,hi) so the small terms meet a small accumulator
             const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
             const CUtensorMap* bm = (P.passes == 3 && pass == 1) ? &P.tmap_b[1] : &P.tmap_b[0];
-            for (int j = j0; j < j1; ++j, ++it) {
-              const uint32_t s = it % stages;
+            for (int j = j0; j < j1; ++j, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
               {
                 ProfTimer pt(prof);
-                wait_mbar(bar_empty + 8 * s, ((it / stages) & 1u) ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
+                wait_mbar(bar_empty + 8 * s, ph ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
                 pt.stop(kProfProducerEmptyWait);
               }
               const uint32_t sa = smem_base + s * kStageBytes;
@@ -614,6 +614,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     if (lane == 0 && pr == 0) {
       constexpr uint32_t idesc = make_idesc<kCG, kTf32>();
       uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
+      uint32_t s = 0, ph = 0;     // ring position: stage and the phase bit of its current use
       for (int i = cta; i < walk.positions; i += num_ctas) {
         if (!walk.at(i).valid) continue;
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
@@ -626,11 +627,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kBlockN;
           const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
-          for (int kb = 0; kb < nkb; ++kb, ++it) {
-            const uint32_t s = it % stages;
+          for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
             {
               ProfTimer pt(prof);
-              wait_mbar(bar_full + 8 * s, (it / stages) & 1u, timeout_ns, kTimeoutFullBar, it);
+              wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it);
               pt.stop(kProfMmaFullWait);
             }
             tc_fence_after();
@@ -675,7 +675,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         const bool pprof = prof && lane == 0;
         ProfTimer push_total(pprof);
 
-        // Lane 0 owns the bulk copies.  Chunks are numbered in issue order (seq = peer slot *
+        // Lane 0 owns the bulk copies; a completed copy group means its writes have been performed,
+        // and the signaller's system-scope fence orders them before the flag.  Chunks are numbered in issue order (seq = peer slot *
         // chunks + chunk).  A finished chunk is handed to the signaller once its stores are known
         // to be written; that check is made kLagPieces pieces later, when it no longer has to
         // wait ("all but the kLagPieces newest copy groups are complete").
@@ -691,7 +692,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         auto settle_all = [&]() {
           ProfTimer pt(pprof);
           bulk_wait_pending<0>();
-          fence_proxy_async_all();
           for (; seq_posted < seq_finished; ++seq_posted) post_chunk(seq_posted);
           pt.stop(kProfPushPublish);
         };
@@ -739,7 +739,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                   cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces)) {
                 ProfTimer pt(pprof);
                 bulk_wait_pending<kLagPieces>();
-                fence_proxy_async_all();
                 while (seq_posted < seq_finished &&
                        cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces))
                   post_chunk(seq_posted++);
@@ -937,7 +936,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         if (pend_old != nullptr) {
           ProfTimer pt(eprof);
           bulk_wait_pending<2 * kPasses>();
-          fence_proxy_async_all();
           pt.stop(kProfEpiFlagWait);
           mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
         }
@@ -949,7 +947,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     if (lane == 0) {
       if (pend_new != nullptr) {
         bulk_wait_pending<0>();
-        fence_proxy_async_all();
         if (pend_old != nullptr)
           mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
         mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_new)), timeout_ns);
@@ -980,7 +977,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // ============================ signaller ============================
     // Lane w serves mailbox w.  A batch of notes costs one system-scope fence; the flag stores
     // after it are relaxed (the fence already orders the landed data before them).
-    if (lane < kMailboxes) {
+    // (nothing is ever posted without an exchange: stay off the issue slots then)
+    if (lane < kMailboxes && P.world > 1 && P.mode != kPlain) {
       volatile Mailbox* mb = &mbox[lane];
       uint32_t done = 0;
       uint64_t idle_since = 0;
@@ -1015,7 +1013,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         } else if (mb->closed) {
           if (mb->ready == done) break;
         } else {
-          __nanosleep(200);
+          __nanosleep(1000);
           if (aborted()) break;
           const uint64_t now = globaltimer_ns();
           if (idle_since == 0) idle_since = now;
