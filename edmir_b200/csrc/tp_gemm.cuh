@@ -365,7 +365,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[2 * kMaxStages + 4 + 2 * kCommWarps];
+  __shared__ uint64_t bars[2 * kMaxStages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ Mailbox mbox[kMailboxes];
   __shared__ uint32_t reduce_next;  // next (half-tile, quarter) unit of the reduction
@@ -390,12 +390,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_empty = smem_u32(&bars[kStages]);
   const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
-  const uint32_t bar_comm = smem_u32(&bars[2 * kMaxStages + 4]);  // [comm warp][buffer]
   // all-gather mode gives the last ring stage to the push warps as staging buffers
   const bool ag_push = P.mode == kAG && P.world > 1;
-  uint32_t stages = ag_push ? kStages - 1 : kStages;
+  uint32_t stages = kStages;
   if (lp.stage_limit > 0 && static_cast<uint32_t>(lp.stage_limit) < stages) stages = lp.stage_limit;
-  const uint32_t smem_comm = smem_base + (kStages - 1) * kStageBytes;
 
   if (threadIdx.x == 32) reduce_next = 0;
   if (threadIdx.x < kMailboxes) {
@@ -406,7 +404,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int a = 0; a < 2 * kCommWarps; ++a) mbar_init(bar_comm + 8 * a, 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
@@ -432,6 +429,63 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const int seg_kb = (P.seg_kblocks > 0 && P.seg_kblocks < num_kb_pass) ? P.seg_kblocks : num_kb_pass;
   const int num_segs = (num_kb_pass + seg_kb - 1) / seg_kb;
   const int rows_per_rank = P.world > 0 ? P.M / P.world : P.M;
+
+  // ------------------------------------------------------------------ all-gather pushes
+  // Five warps per CTA (2, 3, 9, 10, 11) copy the local shard into every peer's gather buffer with
+  // plain 16-byte loads and stores; the TMA queue stays reserved for the operand ring, which a
+  // back-pressured remote bulk store would otherwise hold up.  The stores need no completion
+  // wait: a warp posts "my part of chunk c for peer p is issued" and the signaller's
+  // system-scope fence orders those stores before the flag.
+  constexpr int kPushWarps = 5;
+  auto push_shard = [&](int pw, Mailbox* note_box) {
+    const bool pprof = prof && lane == 0 && pw == 0;
+    ProfTimer push_total(pprof);
+    const int gw = cta_in_rank * kPushWarps + pw;
+    const int total_warps = lp.ctas_per_vrank * kPushWarps;
+    const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
+    const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
+    const int64_t src_ld = P.ld_x * kElemBytes;
+    const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
+    const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
+    const int first_d = P.ag_local_direct ? 1 : 0;
+    // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after its
+    // own), then to rank-2, ...: every GPU sends to and receives from one peer at a time
+    for (int d = first_d; d < P.world; ++d) {
+      const int peer = (P.rank - d + P.world) % P.world;
+      const char* src = static_cast<const char*>(P.x_local);
+      char* dst = static_cast<char*>(P.gather[peer]);
+      for (int c = 0; c < P.ag_chunks; ++c) {
+        const int r_lo = c * chunk_rows;
+        const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
+        const int64_t nvec = static_cast<int64_t>(max(r_hi - r_lo, 0)) * row_vecs;
+        constexpr int kUnroll = 8;
+        for (int64_t v0 = static_cast<int64_t>(gw) * 32 * kUnroll; v0 < nvec;
+             v0 += static_cast<int64_t>(total_warps) * 32 * kUnroll) {
+          uint4 buf[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const int64_t v = v0 + u * 32 + lane;
+            if (v < nvec) {
+              const int64_t row = v / row_vecs, col = v - row * row_vecs;
+              buf[u] = ld_cg_v4(src + (r_lo + row) * src_ld + col * 16);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const int64_t v = v0 + u * 32 + lane;
+            if (v < nvec) {
+              const int64_t row = v / row_vecs, col = v - row * row_vecs;
+              st_global_v4(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, buf[u]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0)
+          mailbox_post(note_box, make_note(kNoteChunk, (static_cast<uint64_t>(peer) << 24) | c), timeout_ns);
+      }
+    }
+    push_total.stop(kProfPushTotal);
+  };
 
   // ------------------------------------------------------------------ reduction of owned tiles
   // Adds up the W partial copies of a 128-row half-tile this rank owns (fp32, fixed rank order,
@@ -552,6 +606,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       tma_prefetch_desc(&P.tmap_a[0]);
       tma_prefetch_desc(&P.tmap_b[0]);
       uint32_t it = 0, s = 0, ph = 0;  // ring position: stage and the phase bit of its current use
+      uint64_t seen_chunks = 0;        // all-gather chunks whose flag this CTA has already acquired
       for (int i = cta; i < walk.positions; i += num_ctas) {
         const Tile t = walk.at(i);
         if (!t.valid) continue;
@@ -569,14 +624,21 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             a_row = m0 - P.rank * rows_per_rank;
           } else {
             ProfTimer pt(prof);
+            bool fresh = false;  // some chunk is seen for the first time by this CTA
             for (int s = s_lo; s <= s_hi; ++s) {
               const int lo = max(m0, s * rows_per_rank) - s * rows_per_rank;
               const int hi = min(m1, (s + 1) * rows_per_rank) - s * rows_per_rank;
-              for (int c = lo / chunk_rows; c <= (hi - 1) / chunk_rows; ++c)
-                wait_flag(P.flags[P.rank] + P.gather_flag_off + s * P.ag_chunks + c, P.epoch,
+              for (int c = lo / chunk_rows; c <= (hi - 1) / chunk_rows; ++c) {
+                const int id = s * P.ag_chunks + c;
+                if (id < 64 && ((seen_chunks >> id) & 1ull)) continue;  // acquired earlier
+                wait_flag(P.flags[P.rank] + P.gather_flag_off + id, P.epoch,
                           timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
+                if (id < 64) seen_chunks |= 1ull << id;
+                fresh = true;
+              }
             }
-            fence_proxy_async_all();  // peer-written rows are read by the async proxy next
+            // rows written by a peer (generic proxy) are read by TMA (async proxy) next
+            if (fresh) fence_proxy_async_global();
             pt.stop(kProfProducerGatherWait);
           }
         }
@@ -653,109 +715,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
   } else if (warp < 2 + kCommWarps) {
     // ============================ all-gather pushes ============================
-    if (ag_push) {
-      // Each push warp moves 8 KiB pieces of the local shard: bulk load into a shared-memory
-      // buffer, bulk store into the peer's gather buffer.  Both are asynchronous; the lane only
-      // blocks on the (local, short) load, so stores stay in flight back to back.  A chunk is
-      // published to its peer once the stores of it are known complete, which is checked one
-      // chunk late (wait for all but the newest groups) so the link never drains for a flag.
-      const int cw = warp - 2;
-      {
-        constexpr uint32_t kPiece = 8192;
-        const int gw = cta_in_rank * kCommWarps + cw;
-        const int total_warps = lp.ctas_per_vrank * kCommWarps;
-        const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
-        const int64_t row_bytes = static_cast<int64_t>(P.K) * kElemBytes;
-        const int64_t src_ld = P.ld_x * kElemBytes;
-        const bool flat = (src_ld == row_bytes);  // shard is one contiguous byte range
-        const int first_d = P.ag_local_direct ? 1 : 0;
-        const uint32_t buf0 = smem_comm + cw * 2 * kPiece;
-        const uint32_t bar0 = bar_comm + cw * 16;
-        uint32_t cnt = 0;             // pieces issued by lane 0
-        const bool pprof = prof && lane == 0;
-        ProfTimer push_total(pprof);
-
-        // Lane 0 owns the bulk copies; a completed copy group means its writes have been performed,
-        // and the signaller's system-scope fence orders them before the flag.  Chunks are numbered in issue order (seq = peer slot *
-        // chunks + chunk).  A finished chunk is handed to the signaller once its stores are known
-        // to be written; that check is made kLagPieces pieces later, when it no longer has to
-        // wait ("all but the kLagPieces newest copy groups are complete").
-        constexpr int kLagPieces = 6;
-        constexpr int kQueue = 8;
-        uint32_t fin_cnt[kQueue];     // value of cnt when chunk (seq % kQueue) was finished
-        int seq_posted = 0, seq_finished = 0;
-        auto post_chunk = [&](int seq) {
-          const int d = first_d + seq / P.ag_chunks, c = seq - (seq / P.ag_chunks) * P.ag_chunks;
-          const int peer = (P.rank - d + P.world) % P.world;
-          mailbox_post(&mbox[4 + cw], make_note(kNoteChunk, (static_cast<uint64_t>(peer) << 24) | c), timeout_ns);
-        };
-        auto settle_all = [&]() {
-          ProfTimer pt(pprof);
-          bulk_wait_pending<0>();
-          for (; seq_posted < seq_finished; ++seq_posted) post_chunk(seq_posted);
-          pt.stop(kProfPushPublish);
-        };
-
-        // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after
-        // its own), then to rank-2, ...: every GPU sends to and receives from one peer at a time
-        for (int d = first_d; d < P.world; ++d) {
-          const int peer = (P.rank - d + P.world) % P.world;
-          const char* src = static_cast<const char*>(P.x_local);
-          char* dst = static_cast<char*>(P.gather[peer]) + static_cast<int64_t>(P.rank) * rows_per_rank * row_bytes;
-          for (int c = 0; c < P.ag_chunks; ++c) {
-            const int r_lo = c * chunk_rows;
-            const int r_hi = min(r_lo + chunk_rows, rows_per_rank);
-            const int64_t rows = max(r_hi - r_lo, 0);
-            // pieces: flat -> 8 KiB slices of the chunk; strided -> slices of each row
-            const int64_t per_row = (row_bytes + kPiece - 1) / kPiece;
-            const int64_t npieces = flat ? (rows * row_bytes + kPiece - 1) / kPiece : rows * per_row;
-            for (int64_t k = gw; k < npieces; k += total_warps) {
-              if (lane == 0) {
-                int64_t s_off, d_off;
-                uint32_t len;
-                if (flat) {
-                  s_off = d_off = r_lo * row_bytes + k * kPiece;
-                  len = static_cast<uint32_t>(min(static_cast<int64_t>(kPiece), rows * row_bytes - k * kPiece));
-                } else {
-                  const int64_t r = k / per_row, part = k - r * per_row;
-                  s_off = (r_lo + r) * src_ld + part * kPiece;
-                  d_off = (r_lo + r) * row_bytes + part * kPiece;
-                  len = static_cast<uint32_t>(min(static_cast<int64_t>(kPiece), row_bytes - part * kPiece));
-                }
-                const uint32_t b = cnt & 1u;
-                ProfTimer pb(pprof);
-                bulk_wait_read_pending<1>();  // the store that last used this buffer has read it
-                pb.stop(kProfPushBufferWait);
-                mbar_arrive_expect_tx(bar0 + 8 * b, len);
-                bulk_load(buf0 + b * kPiece, src + s_off, len, bar0 + 8 * b);
-                ProfTimer pl(pprof);
-                wait_mbar(bar0 + 8 * b, (cnt >> 1) & 1u, timeout_ns, kTimeoutFullBar, 0x80000000u | cnt);
-                pl.stop(kProfPushLoadWait);
-                bulk_store(dst + d_off, buf0 + b * kPiece, len);
-                bulk_commit();
-              }
-              ++cnt;
-              if (lane == 0 && seq_posted < seq_finished &&
-                  cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces)) {
-                ProfTimer pt(pprof);
-                bulk_wait_pending<kLagPieces>();
-                while (seq_posted < seq_finished &&
-                       cnt - fin_cnt[seq_posted % kQueue] >= static_cast<uint32_t>(kLagPieces))
-                  post_chunk(seq_posted++);
-                pt.stop(kProfPushPublish);
-              }
-            }
-            if (lane == 0) {
-              if (seq_finished - seq_posted == kQueue) settle_all();  // queue full
-              fin_cnt[seq_finished % kQueue] = cnt;
-              ++seq_finished;
-            }
-          }
-        }
-        if (lane == 0) settle_all();
-        push_total.stop(kProfPushTotal);
-      }
-    }
+    if (ag_push) push_shard(warp - 2, &mbox[4 + (warp - 2)]);
     if (fused_reduce) {
       // ============================ reducer ============================
       const bool rprof = prof && lane == 0 && warp == 2;
@@ -982,7 +942,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       volatile Mailbox* mb = &mbox[lane];
       uint32_t done = 0;
       uint64_t idle_since = 0;
-      const int total_push_warps = lp.ctas_per_vrank * kCommWarps;
+      const int total_push_warps = lp.ctas_per_vrank * kPushWarps;
       while (true) {
         const uint32_t ready = mb->ready;
         if (ready != done) {
@@ -1022,8 +982,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       }
     }
   } else {
-    // ============================ extra reducers (warps 9-11) ============================
+    // ============================ extra reducers / push warps (warps 9-11) ============================
     if (fused_reduce) reduce_units(&mbox[6 + (warp - 9)], false);
+    if (ag_push) push_shard(2 + (warp - 9), &mbox[6 + (warp - 9)]);
     __syncwarp();
     if (lane == 0) mailbox_close(&mbox[6 + (warp - 9)]);
   }
