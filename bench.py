@@ -251,7 +251,7 @@ def run_ours(args) -> None:
     # per-op times (same launches, timed one op at a time)
     per_op = []
     sub_steps = max(10, args.steps // 4)
-    for o in ops:
+    for o in ([] if args.quick else ops):
         us = timed(lambda o=o: launch(o), sub_steps, 3)
         fl = op_flops(M, o["K"], o["N"])
         wire = nvlink_bytes(o["op"], M, o["K"], o["N"], world)
@@ -279,7 +279,9 @@ def run_ours(args) -> None:
                 linear.gemm(o["xg"], o["b"], o["out"])
             else:
                 linear.gemm(o["a"], o["b"], o["full"])
-    if world > 1:
+    if args.quick:
+        pass
+    elif world > 1:
         for o in ops:
             if o["op"] == "ag_gemm":
                 o["xg"] = torch.empty(M, o["K"], dtype=torch.bfloat16, device=dev)
@@ -308,7 +310,7 @@ def run_ours(args) -> None:
             launch(o)
             o["out_host"].copy_(o["out"], non_blocking=True)
     e2e_steps = max(3, min(args.steps, 20))
-    e2e_us = timed(e2e_step, e2e_steps, 3)
+    e2e_us = None if args.quick else timed(e2e_step, e2e_steps, 3)
     h2d = sum(o["a_host"].numel() * 2 for o in ops)
     d2h = sum(o["out_host"].numel() * 2 for o in ops)
     clocks = sampler.stop() if sampler else None
@@ -331,13 +333,13 @@ def run_ours(args) -> None:
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst)", "kernel": "tp_gemm_kernel<bf16>",
                          "traffic": NCU_TRAFFIC_BYTES_PER_STEP},
             "per_op": per_op,
-            "e2e": {"value": round(e2e_us, 2), "unit": "us/layer", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": None if e2e_us is None else round(e2e_us, 2), "unit": "us/layer", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * len(ops),
             "clocks": clocks,
         }
         line.update(extra)
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.quick:
             threads = os.cpu_count() or 1
             v, desc = cpu_layer_us(M, min(M, 1024), threads)
             line["cpu_baseline"] = {"value": round(v, 1), "unit": "us/layer", "cores": threads, "kind": "port",
@@ -360,6 +362,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--chunks", type=int, default=4, help="all-gather chunks per shard")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true",
+                    help="time the layer only (no per-op, baseline, end-to-end or CPU legs): for profiler runs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
