@@ -86,6 +86,7 @@ SIGNATURES = {
     "edm_gemm_bf16": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_gemm_fp32_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "edm_gemm_fp32": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "edm_gemm_fp32_static": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_comm_create": (C.c_int, [C.c_int, C.c_int, _sz, _sz, C.POINTER(_vp)]),
     "edm_comm_destroy": (C.c_int, [_vp]),
     "edm_comm_export": (C.c_int, [_vp, _vp]),

@@ -258,6 +258,75 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
 
 }  // namespace
 
+// ======================================================================== allocation-free fp32 GEMM
+// Scratch for edm_gemm_fp32_static: the tf32 high/low copies of A and B (first
+// kStaticSplitBytes) followed by one fp32 running-sum tile for each of kStaticCtas CTAs.  The
+// array is part of the library image: every GPU that loads the library keeps these 12 MiB until
+// the process exits.  In host code the name below is only a handle for the runtime, never a
+// device address; the address a kernel may use comes from cudaGetSymbolAddress.
+namespace {
+constexpr size_t kStaticSplitBytes = 8u << 20;
+constexpr int kStaticCtas = 32;
+constexpr size_t kStaticScratchBytes = kStaticSplitBytes + static_cast<size_t>(kStaticCtas) * kBlockM * kBlockN * 4;
+constexpr int kMaxDevices = 64;
+}  // namespace
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+extern "C" int edm_gemm_fp32_static(const void* a, int64_t lda, const void* b, int64_t ldb, void* d,
+                                    int64_t ldd, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (!a || !b || !d) return EDM_ERR_BAD_ARG;
+  int rc = check_dims(M, N, K);
+  if (rc) return rc;
+  if (K % 4 || N % 4 || lda < K || ldb < K || ldd < N) return EDM_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(d) & 15u) || ((ldd * 4) & 15)) return EDM_ERR_BAD_ARG;
+  const size_t a_sz = align_up(static_cast<size_t>(M) * K * 4, 256);
+  const size_t b_sz = align_up(static_cast<size_t>(N) * K * 4, 256);
+  if (2 * (a_sz + b_sz) > kStaticSplitBytes) return EDM_ERR_CAPACITY;  // operands too large for the fixed scratch
+
+  // Set-up, once per device, with that device current: resolve the device address of the array.
+  static char* scratch_of_device[kMaxDevices] = {};
+  int dev = 0;
+  EDM_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return EDM_ERR_UNSUPPORTED;
+  if (scratch_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    EDM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (p == nullptr) return EDM_ERR_CUDA;
+    scratch_of_device[dev] = static_cast<char*>(p);
+  }
+  char* w = scratch_of_device[dev];
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* a_hi = reinterpret_cast<float*>(w);
+  float* a_lo = reinterpret_cast<float*>(w + a_sz);
+  float* b_hi = reinterpret_cast<float*>(w + 2 * a_sz);
+  float* b_lo = reinterpret_cast<float*>(w + 2 * a_sz + b_sz);
+  // both splits and the running sums are fully rewritten by every call: nothing has to start at zero
+  split_tf32_kernel<<<296, 256, 0, s>>>(static_cast<const float*>(a), a_hi, a_lo, M, K, lda);
+  split_tf32_kernel<<<296, 256, 0, s>>>(static_cast<const float*>(b), b_hi, b_lo, N, K, ldb);
+  EDM_CUDA(cudaGetLastError());
+
+  LaunchParams lp;
+  std::memset(&lp, 0, sizeof(lp));
+  RankParams& P = lp.r[0];
+  if ((rc = make_tmap(&P.tmap_a[0], a_hi, M, K, K, 4, kBlockM))) return rc;
+  if ((rc = make_tmap(&P.tmap_a[1], a_lo, M, K, K, 4, kBlockM))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN))) return rc;
+  P.passes = 3;
+  P.seg_kblocks = kSegKBlocks;
+  P.scratch = reinterpret_cast<float*>(w + kStaticSplitBytes);  // indexed by CTA: the grid stays <= kStaticCtas
+  P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
+  P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
+  P.out = d; P.ld_out = ldd;
+  const int64_t tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
+  const int grid = static_cast<int>(tiles < kStaticCtas ? tiles : kStaticCtas);
+  lp.num_vranks = 1;
+  lp.ctas_per_vrank = grid;
+  lp.timeout_ns = g_timeout_ns;
+  return launch_variant(EDM_DTYPE_FP32, 1, lp, grid, false, s);
+}
+
 // ======================================================================== contexts
 struct edm_comm {
   int rank = 0, world = 1;

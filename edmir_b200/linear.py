@@ -90,6 +90,29 @@ def gemm_fp32(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+def gemm_fp32_static(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = a @ b^T`` in fp32 without any allocation: for callers that can neither allocate
+    device memory nor pass a workspace where they need the product.  ``out`` is required (this
+    wrapper does not allocate either).  Scratch is a fixed 12 MiB array inside the library, so
+    ``8 * (M*K + N*K)`` bytes must fit in 8 MiB (``EdmError`` with the capacity code otherwise),
+    calls must not overlap on the GPU, and the first call on a device should precede any
+    stream capture."""
+    _require_cuda(a, b, out)
+    _check_2d(a, "a")
+    _check_2d(b, "b")
+    _check_2d(out, "out")
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or out.dtype != torch.float32:
+        raise ValueError("gemm_fp32_static expects float32 tensors")
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb or tuple(out.shape) != (M, N):
+        raise ValueError("shapes must be a[M,K], b[N,K], out[M,N]")
+    rc = _lib.load().edm_gemm_fp32_static(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                          out.data_ptr(), out.stride(0), M, N, K, _stream())
+    _lib.check(rc, "edm_gemm_fp32_static")
+    return out
+
+
 def tiled_mma_bf16_bf16_bf16_fp32(a: torch.Tensor, b: torch.Tensor,
                                   c: torch.Tensor | None = None) -> torch.Tensor:
     """Drop-in for the reference's only native operator (EDM-IR/ir/c-extension/mma.cu:175,

@@ -84,6 +84,22 @@ int edm_gemm_fp32(const void* a, int64_t lda, const void* b, int64_t ldb, void* 
                   int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
                   void* stream);
 
+/* fp32 GEMM that allocates nothing and needs no workspace argument.  (No counterpart in the
+ * reference.)  It is meant for callers that cannot call cudaMalloc or hand over a scratch
+ * buffer at the point where they need the product -- code running inside another framework's
+ * allocator-owned region, plugin callbacks with a fixed signature, or start-up paths that run
+ * before an allocator exists.  Same arithmetic and accuracy as edm_gemm_fp32; its scratch is a
+ * 12 MiB device array built into the library (held by every GPU that loads the library until the
+ * process exits), which bounds the problem: 8 * (M*K + N*K) bytes (each term rounded up to 256)
+ * must not exceed 8 MiB, otherwise EDM_ERR_CAPACITY is returned and nothing is launched.  The
+ * launch uses at most 32 CTAs, so it is slower than edm_gemm_fp32 on large outputs.
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call before any stream capture begins.  All calls share the one array and it
+ * keeps whatever the last call left; every call rewrites all of it that it reads, but two calls
+ * that overlap on the GPU (different streams, or different threads' streams) race on it. */
+int edm_gemm_fp32_static(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
+                         int64_t M, int64_t N, int64_t K, void* stream);
+
 /* ---- symmetric memory and peer windows ---------------------------------------------
  * No reference counterpart: the reference only names collectives as op strings
  * (EDM-IR/ir/ops.py:32-35) and records `backend` as free text (EDM-IR/ir/uop.py:49).
