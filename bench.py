@@ -214,7 +214,7 @@ def run_ours(args) -> None:
         if world == 1:
             linear.gemm(o["a"], o["b"], o["out"])
         elif o["op"] == "ag_gemm":
-            ctx.ag_gemm(o["a"], o["b"], o["out"], chunks=args.chunks)
+            ctx.ag_gemm(o["a"], o["b"], o["out"], chunks=args.chunks, transport=args.transport)
         else:
             ctx.gemm_rs(o["a"], o["b"], o["out"])
 
@@ -361,6 +361,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--chunks", type=int, default=4, help="all-gather chunks per shard")
+    ap.add_argument("--transport", default="ce", choices=("sm", "ce"),
+                    help="all-gather shards by in-kernel stores (sm) or copy engines (ce)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quick", action="store_true",
                     help="time the layer only (no per-op, baseline, end-to-end or CPU legs): for profiler runs")

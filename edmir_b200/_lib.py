@@ -26,6 +26,9 @@ EDM_OP_GEMM_RS = 1
 EDM_OP_GEMM_AR = 2
 EDM_OP_AG_GEMM = 3
 
+EDM_TRANSPORT_SM = 0
+EDM_TRANSPORT_COPY_ENGINE = 1
+
 EDM_MAX_RANKS = 8
 EDM_IPC_HANDLE_BYTES = 64
 
@@ -48,7 +51,7 @@ class TpCall(C.Structure):
         ("b", C.c_void_p), ("ldb", C.c_int64),
         ("d", C.c_void_p), ("ldd", C.c_int64),
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
-        ("chunks", C.c_int32), ("reserved", C.c_int32),
+        ("chunks", C.c_int32), ("transport", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 

@@ -47,6 +47,20 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+using WriteValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+WriteValue32Fn write_value_fn() {
+  static WriteValue32Fn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<WriteValue32Fn>(p);
+  });
+  return fn;
+}
+
 // K-major matrix [rows, k] with leading dimension ld (elements); box = 128 bytes of K x box_rows.
 int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes,
               int box_rows) {
@@ -253,6 +267,8 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
+  lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
   return launch_variant(dtype, cg, lp, grid, false, s);
 }
 
@@ -340,6 +356,9 @@ struct edm_comm {
   size_t heap_used = 0;
   size_t total_bytes = 0;
   uint32_t epoch = 0;
+  // copy-engine transport of the all-gather: a side stream and the events that tie it to the caller's
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_in = nullptr, ev_out = nullptr;
 
   size_t off_flags() const { return 0; }
   size_t off_counters() const { return flag_bytes; }
@@ -452,6 +471,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     P.ag_chunks = call.chunks;
     P.ag_local_direct = (rows % kBlockM == 0) ? 1 : 0;
     P.x_local = call.a; P.ld_x = call.lda;
+    P.ag_external = call.transport == EDM_TRANSPORT_COPY_ENGINE ? 1 : 0;
     P.passes = 1;
     // A comes from the local gather buffer [M,K]; the own shard is read in place when it
     // covers whole row blocks
@@ -475,6 +495,48 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     if (rc) return rc;
   }
   c->epoch = epoch;
+  return EDM_OK;
+}
+
+// Copy-engine transport of one all-gather: after the caller's stream has produced the shard, the
+// side stream copies it into every peer's gather buffer chunk by chunk (peer order rank-1,
+// rank-2, ...: every GPU sends to and receives from one peer at a time) and raises each chunk's
+// flag with a stream-ordered 32-bit write, which cannot overtake the copy before it.  No SM takes
+// part, so the GEMM's operand traffic is not disturbed.  `after_launch` closes the bracket: later
+// work on the caller's stream waits until the outgoing copies have read the shard.
+int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) {
+  WriteValue32Fn wv = write_value_fn();
+  if (!wv) return EDM_ERR_UNSUPPORTED;
+  const int W = P.world;
+  const int64_t rows = P.M / W;
+  const int elem = 2;
+  const size_t row_bytes = static_cast<size_t>(P.K) * elem;
+  const int64_t chunk_rows = (rows + P.ag_chunks - 1) / P.ag_chunks;
+  EDM_CUDA(cudaEventRecord(c->ev_in, stream));
+  EDM_CUDA(cudaStreamWaitEvent(c->side, c->ev_in, 0));
+  // when the shard does not cover whole row blocks the kernel also reads the own rows from the
+  // gather buffer: deliver them (d = 0) like a peer's
+  for (int d = P.ag_local_direct ? 1 : 0; d < W; ++d) {
+    const int peer = (P.rank - d + W) % W;
+    char* dst0 = static_cast<char*>(P.gather[peer]) + static_cast<size_t>(P.rank) * rows * row_bytes;
+    const char* src0 = static_cast<const char*>(P.x_local);
+    for (int ch = 0; ch < P.ag_chunks; ++ch) {
+      const int64_t r_lo = ch * chunk_rows;
+      const int64_t r_hi = r_lo + chunk_rows < rows ? r_lo + chunk_rows : rows;
+      if (r_hi > r_lo)
+        EDM_CUDA(cudaMemcpy2DAsync(dst0 + r_lo * row_bytes, row_bytes, src0 + r_lo * P.ld_x * elem,
+                                   static_cast<size_t>(P.ld_x) * elem, row_bytes, static_cast<size_t>(r_hi - r_lo),
+                                   cudaMemcpyDeviceToDevice, c->side));
+      uint32_t* flag = P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + ch;
+      CUresult r = wv(reinterpret_cast<CUstream>(c->side), reinterpret_cast<CUdeviceptr>(flag), P.epoch, 0);
+      if (r != CUDA_SUCCESS) { g_last_cuda_error = 100000 + static_cast<int>(r); return EDM_ERR_CUDA; }
+    }
+  }
+  return EDM_OK;
+}
+int ag_copy_engine_after_launch(edm_comm* c, cudaStream_t stream) {
+  EDM_CUDA(cudaEventRecord(c->ev_out, c->side));
+  EDM_CUDA(cudaStreamWaitEvent(stream, c->ev_out, 0));
   return EDM_OK;
 }
 
@@ -554,6 +616,13 @@ int edm_comm_create(int rank, int world, size_t window_bytes, size_t heap_bytes,
   e = cudaMemset(p, 0, c->flag_bytes + c->counter_bytes);
   if (e != cudaSuccess) { g_last_cuda_error = e; cudaFree(p); delete c; return EDM_ERR_CUDA; }
   c->base[rank] = static_cast<char*>(p);
+  if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->ev_in, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&c->ev_out, cudaEventDisableTiming) != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(cudaGetLastError());
+    edm_comm_destroy(c);
+    return EDM_ERR_CUDA;
+  }
   *out = c;
   return EDM_OK;
 }
@@ -564,6 +633,9 @@ int edm_comm_destroy(edm_comm_t* c) {
   for (int p = 0; p < c->world; ++p)
     if (c->imported[p] && c->base[p]) cudaIpcCloseMemHandle(c->base[p]);
   if (c->base[c->rank]) cudaFree(c->base[c->rank]);
+  if (c->ev_in) cudaEventDestroy(c->ev_in);
+  if (c->ev_out) cudaEventDestroy(c->ev_out);
+  if (c->side) cudaStreamDestroy(c->side);
   delete c;
   return EDM_OK;
 }
@@ -650,7 +722,14 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
-  return launch_variant(call->dtype, cg, lp, grid, false, s);
+  lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
+  const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
+  if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
+  rc = launch_variant(call->dtype, cg, lp, grid, false, s);
+  if (rc) return rc;
+  if (ce) return ag_copy_engine_after_launch(comm, s);
+  return EDM_OK;
 }
 
 int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls, int n, void* stream) {
@@ -678,7 +757,15 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
-  return launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
+  lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
+  for (int i = 0; i < n; ++i)
+    if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
+  rc = launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
+  if (rc) return rc;
+  for (int i = 0; i < n; ++i)
+    if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_after_launch(comms[i], s))) return rc;
+  return EDM_OK;
 }
 
 static int tp_bf16(edm_comm_t* comm, int op, const void* a, int64_t lda, const void* b, int64_t ldb,
@@ -687,7 +774,7 @@ static int tp_bf16(edm_comm_t* comm, int op, const void* a, int64_t lda, const v
   std::memset(&c, 0, sizeof(c));
   c.op = op; c.dtype = EDM_DTYPE_BF16;
   c.a = a; c.lda = lda; c.b = b; c.ldb = ldb; c.d = d; c.ldd = ldd;
-  c.M = M; c.N = N; c.K = K; c.chunks = chunks;
+  c.M = M; c.N = N; c.K = K; c.chunks = chunks; c.transport = EDM_TRANSPORT_SM;
   return edm_tp_launch(comm, &c, stream);
 }
 int edm_gemm_rs_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b, int64_t ldb,

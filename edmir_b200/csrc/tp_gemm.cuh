@@ -100,7 +100,7 @@ struct alignas(64) RankParams {
   uint32_t* counters;      // AG: local arrival counters [world*ag_chunks]
   float* scratch;          // split-fp32: running fp32 sums, one kBlockM x kBlockN tile per CTA
   int32_t seg_kblocks;     // split-fp32: K blocks accumulated in TMEM before folding into scratch (0 = all)
-  int32_t pad0;
+  int32_t ag_external;     // AG: shards and chunk flags are delivered by copy engines, not by this kernel
   void* peer_out[kMaxRanks];   // AR: every rank's output as mapped here
   char* win[kMaxRanks];        // every rank's window (parity half already selected)
   uint32_t* flags[kMaxRanks];  // every rank's flag array
@@ -113,6 +113,8 @@ struct LaunchParams {
   uint64_t timeout_ns;
   int32_t profile;        // 1: accumulate per-role wait times into g_prof
   int32_t stage_limit;    // experiments: use at most this many ring stages (0 = all)
+  int32_t push_stride;    // all-gather: only CTAs whose index is a multiple of this push the shard
+  int32_t pad1;
   RankParams r[kMaxVirtualRanks];
 };
 
@@ -391,7 +393,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
   // all-gather mode gives the last ring stage to the push warps as staging buffers
-  const bool ag_push = P.mode == kAG && P.world > 1;
+  const bool ag_push = P.mode == kAG && P.world > 1 && !P.ag_external;
   uint32_t stages = kStages;
   if (lp.stage_limit > 0 && static_cast<uint32_t>(lp.stage_limit) < stages) stages = lp.stage_limit;
 
@@ -440,8 +442,13 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   auto push_shard = [&](int pw, Mailbox* note_box) {
     const bool pprof = prof && lane == 0 && pw == 0;
     ProfTimer push_total(pprof);
-    const int gw = cta_in_rank * kPushWarps + pw;
-    const int total_warps = lp.ctas_per_vrank * kPushWarps;
+    // pushing CTAs: every push_stride-th one (remote stores that queue up behind a busy link also
+    // delay the operand loads of the SM that issued them, so the duty is kept to a subset)
+    const int stride = max(lp.push_stride, 1);
+    if (cta_in_rank % stride != 0) return;
+    const int pushers = (lp.ctas_per_vrank + stride - 1) / stride;
+    const int gw = (cta_in_rank / stride) * kPushWarps + pw;
+    const int total_warps = pushers * kPushWarps;
     const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
     const int64_t row_vecs = static_cast<int64_t>(P.K) * kElemBytes / 16;  // 16B vectors per row
     const int64_t src_ld = P.ld_x * kElemBytes;
@@ -631,14 +638,20 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
               for (int c = lo / chunk_rows; c <= (hi - 1) / chunk_rows; ++c) {
                 const int id = s * P.ag_chunks + c;
                 if (id < 64 && ((seen_chunks >> id) & 1ull)) continue;  // acquired earlier
+                ProfTimer pa(prof);
                 wait_flag(P.flags[P.rank] + P.gather_flag_off + id, P.epoch,
                           timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
+                pa.stop(20);
                 if (id < 64) seen_chunks |= 1ull << id;
                 fresh = true;
               }
             }
             // rows written by a peer (generic proxy) are read by TMA (async proxy) next
-            if (fresh) fence_proxy_async_global();
+            if (fresh) {
+              ProfTimer pf(prof);
+              fence_proxy_async_global();
+              pf.stop(21);
+            }
             pt.stop(kProfProducerGatherWait);
           }
         }
@@ -938,11 +951,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // Lane w serves mailbox w.  A batch of notes costs one system-scope fence; the flag stores
     // after it are relaxed (the fence already orders the landed data before them).
     // (nothing is ever posted without an exchange: stay off the issue slots then)
-    if (lane < kMailboxes && P.world > 1 && P.mode != kPlain) {
+    if (lane < kMailboxes && P.world > 1 && P.mode != kPlain && !(P.mode == kAG && P.ag_external)) {
       volatile Mailbox* mb = &mbox[lane];
       uint32_t done = 0;
       uint64_t idle_since = 0;
-      const int total_push_warps = lp.ctas_per_vrank * kPushWarps;
+      const int total_push_warps = (lp.ctas_per_vrank + max(lp.push_stride, 1) - 1) / max(lp.push_stride, 1) * kPushWarps;
       while (true) {
         const uint32_t ready = mb->ready;
         if (ready != done) {

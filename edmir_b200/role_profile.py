@@ -1,7 +1,7 @@
 """Per-role device time of the fused launches (where a launch spends its time).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
-        --master-port 29530 -m edmir_b200.role_profile [--tokens 8192] [--chunks 2] [--probe]
+        --master-port 29530 -m edmir_b200.role_profile [--tokens 8192] [--chunks 2] [--transport sm|ce] [--probe]
 
 For each linear of the benchmark layer (qkv, gate_up: all-gather+GEMM; o_proj, down:
 GEMM+reduce-scatter; TP=8-local extents) it prints the launch time and, from the library's
@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--chunks", type=int, default=2)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--probe", action="store_true")
+    ap.add_argument("--transport", default="sm", choices=("sm", "ce"), help="how all-gather shards travel")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
@@ -57,7 +58,7 @@ def main() -> None:
         linear.profile_enable(False)
         ctas = max(prof["ctas"], 1)
         if rank == 0:
-            per = {k: round(v / ctas / 1e3, 1) for k, v in prof.items() if v and k != "ctas" and not k.startswith("r2")}
+            per = {k: round(v / ctas / 1e3, 1) for k, v in prof.items() if v and k != "ctas" }
             print(f"{label}: {e0.elapsed_time(e1) / args.iters * 1e3:.1f} us/launch  per-CTA us: {per}", flush=True)
 
     for name, op, K, N in LAYER:
@@ -69,7 +70,8 @@ def main() -> None:
         plain_out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         if world > 1:
             if op == "ag_gemm":
-                measure(f"{name} {op} tp{world} chunks{args.chunks}", lambda: ctx.ag_gemm(a, b, out, chunks=args.chunks))
+                measure(f"{name} {op} tp{world} chunks{args.chunks} {args.transport}",
+                        lambda: ctx.ag_gemm(a, b, out, chunks=args.chunks, transport=args.transport))
             else:
                 measure(f"{name} {op} tp{world}", lambda: ctx.gemm_rs(a, b, out))
         measure(f"{name} gemm only", lambda: linear.gemm(full_a, b, plain_out))

@@ -21,6 +21,7 @@ from . import _lib
 from .linear import _check_2d, _require_cuda, _stream
 
 _OPS = {"gemm_rs": _lib.EDM_OP_GEMM_RS, "gemm_ar": _lib.EDM_OP_GEMM_AR, "ag_gemm": _lib.EDM_OP_AG_GEMM}
+_TRANSPORTS = {"sm": _lib.EDM_TRANSPORT_SM, "ce": _lib.EDM_TRANSPORT_COPY_ENGINE}
 _DTYPES = {torch.bfloat16: _lib.EDM_DTYPE_BF16, torch.float32: _lib.EDM_DTYPE_FP32}
 
 
@@ -103,7 +104,7 @@ class SymmetricContext:
         _lib.check(self._lib.edm_comm_p2p_probe(self._h, peer, nbytes, mode, _stream()), "edm_comm_p2p_probe")
 
     # ---------------------------------------------------------------- launches
-    def _call(self, op: str, a, b, out, chunks: int = 1) -> "_lib.TpCall":
+    def _call(self, op: str, a, b, out, chunks: int = 1, transport: str = "sm") -> "_lib.TpCall":
         _require_cuda(a, b, out)
         for t, n in ((a, "a"), (b, "b"), (out, "out")):
             _check_2d(t, n)
@@ -123,6 +124,9 @@ class SymmetricContext:
         call.d, call.ldd = out.data_ptr(), out.stride(0)
         call.M, call.N, call.K = M, N, K
         call.chunks = chunks
+        if transport not in _TRANSPORTS:
+            raise ValueError(f"transport must be one of {sorted(_TRANSPORTS)}")
+        call.transport = _TRANSPORTS[transport]
         if a.dtype == torch.float32:
             need = int(self._lib.edm_gemm_fp32_workspace_bytes(a.shape[0], N, K))
             if self._workspace is None or self._workspace.numel() < need:
@@ -130,8 +134,8 @@ class SymmetricContext:
             call.workspace, call.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
         return call
 
-    def _launch(self, op: str, a, b, out, chunks: int = 1):
-        call = self._call(op, a, b, out, chunks)
+    def _launch(self, op: str, a, b, out, chunks: int = 1, transport: str = "sm"):
+        call = self._call(op, a, b, out, chunks, transport)
         _lib.check(self._lib.edm_tp_launch(self._h, C.byref(call), _stream()), f"edm_tp_launch({op})")
         return out
 
@@ -150,11 +154,13 @@ class SymmetricContext:
         return self._launch("gemm_ar", a, b, out)
 
     def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-                chunks: int = 1) -> torch.Tensor:
-        """All-gather of the token-sharded ``x[M/W, K]`` fused with ``out[M, N/W] = X @ w^T``."""
+                chunks: int = 1, transport: str = "sm") -> torch.Tensor:
+        """All-gather of the token-sharded ``x[M/W, K]`` fused with ``out[M, N/W] = X @ w^T``.
+        ``transport="sm"``: warps of the GEMM kernel push the shard; ``"ce"``: copy engines on the
+        library's side stream deliver it and the kernel only waits for the chunk flags."""
         if out is None:
             out = torch.empty((x.shape[0] * self.world, w.shape[0]), dtype=x.dtype, device=x.device)
-        return self._launch("ag_gemm", x, w, out, chunks)
+        return self._launch("ag_gemm", x, w, out, chunks, transport)
 
 
 class EmulatedGroup:
@@ -171,10 +177,10 @@ class EmulatedGroup:
                 if a is not b:
                     _lib.check(lib.edm_comm_link_local(a._h, b.rank, b._h), "edm_comm_link_local")
 
-    def run(self, op: str, a_list, b_list, out_list, chunks: int = 1):
+    def run(self, op: str, a_list, b_list, out_list, chunks: int = 1, transport: str = "sm"):
         calls = (_lib.TpCall * self.world)()
         for r, ctx in enumerate(self.ranks):
-            calls[r] = ctx._call(op, a_list[r], b_list[r], out_list[r], chunks)
+            calls[r] = ctx._call(op, a_list[r], b_list[r], out_list[r], chunks, transport)
         handles = (C.c_void_p * self.world)(*[ctx._h for ctx in self.ranks])
         lib = self.ranks[0]._lib
         _lib.check(lib.edm_tp_launch_emulated(handles, calls, self.world, _stream()),

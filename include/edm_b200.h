@@ -39,6 +39,13 @@ extern "C" {
 #define EDM_OP_GEMM_AR 2 /* row-parallel linear + all-reduce: every rank gets sum_r A_r B_r^T */
 #define EDM_OP_AG_GEMM 3 /* all-gather of token-sharded X, then D_r = X * W_r^T */
 
+/* How the shards of an all-gather travel.  SM: warps of the GEMM kernel store them into the peers'
+ * windows.  COPY_ENGINE: the library's side stream copies them (cudaMemcpy2DAsync) and raises the
+ * chunk flags with stream-ordered 32-bit writes; the kernel only waits for the flags.  The copy
+ * engines do not compete with the GEMM for the SMs' memory pipelines. */
+#define EDM_TRANSPORT_SM 0
+#define EDM_TRANSPORT_COPY_ENGINE 1
+
 #define EDM_MAX_RANKS 8
 #define EDM_IPC_HANDLE_BYTES 64
 
@@ -142,7 +149,7 @@ typedef struct {
   int64_t ldd;
   int64_t M, N, K; /* per-rank GEMM extents; for AG_GEMM M counts the gathered rows */
   int32_t chunks;  /* AG_GEMM: chunks per shard (>= 1); ignored otherwise */
-  int32_t reserved;
+  int32_t transport; /* AG_GEMM: EDM_TRANSPORT_*; ignored otherwise */
   void* workspace; /* EDM_DTYPE_FP32 only: tf32 split scratch */
   size_t workspace_bytes;
 } edm_tp_call_t;

@@ -44,11 +44,15 @@ def main() -> int:
              ("gemm_ar", 1, 4096, 1792, torch.bfloat16, 1),
              ("ag_gemm", 256 * world, 520, 512, torch.bfloat16, 2),
              ("ag_gemm", 64 * world, 256, 128, torch.bfloat16, 1),
+             ("ag_gemm_ce", 256 * world, 520, 512, torch.bfloat16, 2),
              ("gemm_ar", 256, 1024, 512, torch.float32, 1)]
     if big:
-        cases += [("gemm_rs", 8192, 8192, 1024, torch.bfloat16, 1), ("ag_gemm", 8192, 1280, 8192, torch.bfloat16, 4)]
+        cases += [("gemm_rs", 8192, 8192, 1024, torch.bfloat16, 1), ("ag_gemm", 8192, 1280, 8192, torch.bfloat16, 4),
+                  ("ag_gemm_ce", 8192, 1280, 8192, torch.bfloat16, 2)]
     for idx, (op, M, N, K, dtype, chunks) in enumerate(cases):
         wscale = 1.0 if dtype == torch.float32 else 0.02
+        transport = "ce" if op.endswith("_ce") else "sm"
+        op = op.replace("_ce", "")
         rows = M // world if op == "ag_gemm" else M
         a_all = [rand((rows, K), 1.0, dtype, 1000 * idx + r) for r in range(world)]
         b_all = [rand((N, K), wscale, dtype, 1000 * idx + 500 + r) for r in range(world)]
@@ -62,7 +66,7 @@ def main() -> int:
             elif op == "gemm_ar":
                 out = ctx.gemm_ar(a, b, out)
             else:
-                out = ctx.ag_gemm(a, b, chunks=chunks)
+                out = ctx.ag_gemm(a, b, chunks=chunks, transport=transport)
             torch.cuda.synchronize()
             err = oracle.rel_l2(npf(out), want_all[rank])
             tol = FP32_TOL if dtype == torch.float32 else BF16_TOL

@@ -99,9 +99,10 @@ def test_config1_all_reduce_fp32(cuda_clean, group_factory):
         assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("transport", ["sm", "ce"])
 @pytest.mark.parametrize("world,M,N,K,chunks", [(2, 512, 512, 256, 2), (4, 2048, 768, 512, 4), (4, 256, 768, 512, 1),
                                                 (2, 1024, 264, 1000, 3), (4, 4096, 512, 1024, 8)])
-def test_all_gather_gemm(cuda_clean, group_factory, world, M, N, K, chunks):
+def test_all_gather_gemm(cuda_clean, group_factory, world, M, N, K, chunks, transport):
     g = group_factory(world)
     x = [_rand((M // world, K), 1.0, torch.bfloat16, 500 + r) for r in range(world)]
     w = [_rand((N, K), 0.02, torch.bfloat16, 600 + r) for r in range(world)]
@@ -111,7 +112,7 @@ def test_all_gather_gemm(cuda_clean, group_factory, world, M, N, K, chunks):
     for call in range(3):
         for o in outs:
             o.zero_()
-        g.run("ag_gemm", x_d, w_d, outs, chunks)
+        g.run("ag_gemm", x_d, w_d, outs, chunks, transport)
         torch.cuda.synchronize()
         for r in range(world):
             assert oracle.rel_l2(_np(outs[r]), want[r]) <= BF16_TOL, (call, r)
