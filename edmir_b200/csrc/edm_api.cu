@@ -357,8 +357,10 @@ struct edm_comm {
   size_t total_bytes = 0;
   uint32_t epoch = 0;
   // copy-engine transport of the all-gather: a side stream and the events that tie it to the caller's
-  cudaStream_t side = nullptr;
-  cudaEvent_t ev_in = nullptr, ev_out = nullptr;
+  // (several streams so that copies to different peers run on different copy engines at once)
+  static constexpr int kSideStreams = 4;
+  cudaStream_t side[kSideStreams] = {};
+  cudaEvent_t ev_in = nullptr, ev_out[kSideStreams] = {};
 
   size_t off_flags() const { return 0; }
   size_t off_counters() const { return flag_bytes; }
@@ -512,31 +514,43 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) 
   const int elem = 2;
   const size_t row_bytes = static_cast<size_t>(P.K) * elem;
   const int64_t chunk_rows = (rows + P.ag_chunks - 1) / P.ag_chunks;
+  int nstreams = 2;
+  if (const char* e = std::getenv("EDM_SIDE_STREAMS")) nstreams = std::atoi(e);
+  if (nstreams < 1) nstreams = 1;
+  if (nstreams > edm_comm::kSideStreams) nstreams = edm_comm::kSideStreams;
   EDM_CUDA(cudaEventRecord(c->ev_in, stream));
-  EDM_CUDA(cudaStreamWaitEvent(c->side, c->ev_in, 0));
+  for (int i = 0; i < edm_comm::kSideStreams; ++i) EDM_CUDA(cudaStreamWaitEvent(c->side[i], c->ev_in, 0));
   // when the shard does not cover whole row blocks the kernel also reads the own rows from the
   // gather buffer: deliver them (d = 0) like a peer's
   for (int d = P.ag_local_direct ? 1 : 0; d < W; ++d) {
     const int peer = (P.rank - d + W) % W;
+    cudaStream_t side = c->side[d % nstreams];
     char* dst0 = static_cast<char*>(P.gather[peer]) + static_cast<size_t>(P.rank) * rows * row_bytes;
     const char* src0 = static_cast<const char*>(P.x_local);
     for (int ch = 0; ch < P.ag_chunks; ++ch) {
       const int64_t r_lo = ch * chunk_rows;
       const int64_t r_hi = r_lo + chunk_rows < rows ? r_lo + chunk_rows : rows;
-      if (r_hi > r_lo)
-        EDM_CUDA(cudaMemcpy2DAsync(dst0 + r_lo * row_bytes, row_bytes, src0 + r_lo * P.ld_x * elem,
-                                   static_cast<size_t>(P.ld_x) * elem, row_bytes, static_cast<size_t>(r_hi - r_lo),
-                                   cudaMemcpyDeviceToDevice, c->side));
+      if (r_hi > r_lo) {
+        if (P.ld_x == P.K)  // contiguous shard: a plain copy is the fastest thing a copy engine does
+          EDM_CUDA(cudaMemcpyAsync(dst0 + r_lo * row_bytes, src0 + r_lo * row_bytes,
+                                   static_cast<size_t>(r_hi - r_lo) * row_bytes, cudaMemcpyDeviceToDevice, side));
+        else
+          EDM_CUDA(cudaMemcpy2DAsync(dst0 + r_lo * row_bytes, row_bytes, src0 + r_lo * P.ld_x * elem,
+                                     static_cast<size_t>(P.ld_x) * elem, row_bytes, static_cast<size_t>(r_hi - r_lo),
+                                     cudaMemcpyDeviceToDevice, side));
+      }
       uint32_t* flag = P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + ch;
-      CUresult r = wv(reinterpret_cast<CUstream>(c->side), reinterpret_cast<CUdeviceptr>(flag), P.epoch, 0);
+      CUresult r = wv(reinterpret_cast<CUstream>(side), reinterpret_cast<CUdeviceptr>(flag), P.epoch, 0);
       if (r != CUDA_SUCCESS) { g_last_cuda_error = 100000 + static_cast<int>(r); return EDM_ERR_CUDA; }
     }
   }
   return EDM_OK;
 }
 int ag_copy_engine_after_launch(edm_comm* c, cudaStream_t stream) {
-  EDM_CUDA(cudaEventRecord(c->ev_out, c->side));
-  EDM_CUDA(cudaStreamWaitEvent(stream, c->ev_out, 0));
+  for (int i = 0; i < edm_comm::kSideStreams; ++i) {
+    EDM_CUDA(cudaEventRecord(c->ev_out[i], c->side[i]));
+    EDM_CUDA(cudaStreamWaitEvent(stream, c->ev_out[i], 0));
+  }
   return EDM_OK;
 }
 
@@ -616,9 +630,11 @@ int edm_comm_create(int rank, int world, size_t window_bytes, size_t heap_bytes,
   e = cudaMemset(p, 0, c->flag_bytes + c->counter_bytes);
   if (e != cudaSuccess) { g_last_cuda_error = e; cudaFree(p); delete c; return EDM_ERR_CUDA; }
   c->base[rank] = static_cast<char*>(p);
-  if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->ev_in, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&c->ev_out, cudaEventDisableTiming) != cudaSuccess) {
+  bool ok = cudaEventCreateWithFlags(&c->ev_in, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; ok && i < edm_comm::kSideStreams; ++i)
+    ok = cudaStreamCreateWithFlags(&c->side[i], cudaStreamNonBlocking) == cudaSuccess &&
+         cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
     g_last_cuda_error = static_cast<int>(cudaGetLastError());
     edm_comm_destroy(c);
     return EDM_ERR_CUDA;
@@ -634,8 +650,10 @@ int edm_comm_destroy(edm_comm_t* c) {
     if (c->imported[p] && c->base[p]) cudaIpcCloseMemHandle(c->base[p]);
   if (c->base[c->rank]) cudaFree(c->base[c->rank]);
   if (c->ev_in) cudaEventDestroy(c->ev_in);
-  if (c->ev_out) cudaEventDestroy(c->ev_out);
-  if (c->side) cudaStreamDestroy(c->side);
+  for (int i = 0; i < edm_comm::kSideStreams; ++i) {
+    if (c->ev_out[i]) cudaEventDestroy(c->ev_out[i]);
+    if (c->side[i]) cudaStreamDestroy(c->side[i]);
+  }
   delete c;
   return EDM_OK;
 }

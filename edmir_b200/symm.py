@@ -154,7 +154,7 @@ class SymmetricContext:
         return self._launch("gemm_ar", a, b, out)
 
     def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-                chunks: int = 1, transport: str = "sm") -> torch.Tensor:
+                chunks: int = 1, transport: str = "ce") -> torch.Tensor:
         """All-gather of the token-sharded ``x[M/W, K]`` fused with ``out[M, N/W] = X @ w^T``.
         ``transport="sm"``: warps of the GEMM kernel push the shard; ``"ce"``: copy engines on the
         library's side stream deliver it and the kernel only waits for the chunk flags."""
