@@ -268,6 +268,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
   if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
   return launch_variant(dtype, cg, lp, grid, false, s);
 }
@@ -741,6 +742,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
   if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
   const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
   if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
@@ -776,6 +778,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   lp.profile = g_profile;
   if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
   lp.push_stride = 1;
+  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
   if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;

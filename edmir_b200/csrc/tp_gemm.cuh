@@ -114,7 +114,7 @@ struct LaunchParams {
   int32_t profile;        // 1: accumulate per-role wait times into g_prof
   int32_t stage_limit;    // experiments: use at most this many ring stages (0 = all)
   int32_t push_stride;    // all-gather: only CTAs whose index is a multiple of this push the shard
-  int32_t pad1;
+  int32_t band;           // row blocks per band of the tile walk (0 = default)
   RankParams r[kMaxVirtualRanks];
 };
 
@@ -133,23 +133,26 @@ __device__ __forceinline__ bool aborted() {
   return *reinterpret_cast<volatile uint32_t*>(&g_status[0]) != 0u;
 }
 
+// prof_slot >= 0: add the time spent here to that accounting slot (only the slow path pays for it)
 __device__ __noinline__ void wait_mbar_slow(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
-                                            uint32_t code, uint32_t info) {
+                                            uint32_t code, uint32_t info, int prof_slot) {
+  const uint64_t start = prof_slot >= 0 ? globaltimer_ns() : 0;
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((spins++ & 15u) == 0u) {
-      if (aborted()) return;
+      if (aborted()) break;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > timeout_ns) { report(code, info, parity, bar); return; }
+      else if (now - t0 > timeout_ns) { report(code, info, parity, bar); break; }
     }
   }
+  if (prof_slot >= 0) atomicAdd(&g_prof[prof_slot], static_cast<unsigned long long>(globaltimer_ns() - start));
 }
 __device__ __forceinline__ void wait_mbar(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
-                                          uint32_t code, uint32_t info) {
+                                          uint32_t code, uint32_t info, int prof_slot = -1) {
   if (mbar_try_wait(bar, parity)) return;
-  wait_mbar_slow(bar, parity, timeout_ns, code, info);
+  wait_mbar_slow(bar, parity, timeout_ns, code, info, prof_slot);
 }
 
 // Wait until *flag (written by another GPU / CTA with release.sys) has reached `epoch`.
@@ -177,10 +180,9 @@ struct Tile {
   bool valid;     // false for a hole in the walk (all-reduce with a tile count not divisible by world)
 };
 
-// Walk an (mb x nb) grid in bands of 8 row-blocks so that concurrently running CTAs share
-// A and B panels in L2.
-__device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n) {
-  constexpr int kBand = 8;
+// Walk an (mb x nb) grid in bands of kBand row-blocks so that concurrently running CTAs share
+// A and B panels in L2 (taller bands re-read B less often; 16 measured best on the layer's shapes).
+__device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n, int kBand = 8) {
   const int per_band = kBand * nb;
   const int band = i / per_band;
   const int first = band * kBand;
@@ -195,10 +197,12 @@ struct TileWalk {
   int m_blocks, n_blocks, total;
   int positions;    // length of the walk (>= total when it has holes)
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
+  int band;         // row blocks per band of the walk
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
-  __device__ TileWalk(const RankParams& p, int tile_m) {
+  __device__ TileWalk(const RankParams& p, int tile_m, int band_rows) {
     mode = p.mode; rank = p.rank; world = p.world;
+    band = band_rows > 0 ? band_rows : 16;  // 16 x 256 rows of A stay in L2 while B streams through once per band
     m_blocks = (p.M + tile_m - 1) / tile_m;
     n_blocks = (p.N + kBlockN - 1) / kBlockN;
     total = m_blocks * n_blocks;
@@ -218,7 +222,7 @@ struct TileWalk {
   __device__ void owned_tile(int r, int idx, int& m_blk, int& n_blk) const {
     if (mode == kRS) {
       int lm;
-      band_order(idx, mb_per_rank, n_blocks, lm, n_blk);
+      band_order(idx, mb_per_rank, n_blocks, lm, n_blk, band);
       m_blk = r * mb_per_rank + lm;
     } else {
       const int lin = idx * world + r;
@@ -242,13 +246,13 @@ struct TileWalk {
       owned_tile(t.owner, round, t.m_blk, t.n_blk);
     } else if (mode == kAG && mb_per_rank > 0) {
       int pm, n;
-      band_order(i, m_blocks, n_blocks, pm, n);
+      band_order(i, m_blocks, n_blocks, pm, n, band);
       t.m_blk = (rank * mb_per_rank + pm) % m_blocks;  // own shard first, then rank+1, ...
       t.n_blk = n;
       t.owner = rank;
       t.owned_idx = 0;
     } else {
-      band_order(i, m_blocks, n_blocks, t.m_blk, t.n_blk);
+      band_order(i, m_blocks, n_blocks, t.m_blk, t.n_blk, band);
       t.owner = rank;
       t.owned_idx = 0;
     }
@@ -423,7 +427,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P, kBlockM * kCG);
+  const TileWalk walk(P, kBlockM * kCG, lp.band);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -614,6 +618,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       tma_prefetch_desc(&P.tmap_b[0]);
       uint32_t it = 0, s = 0, ph = 0;  // ring position: stage and the phase bit of its current use
       uint64_t seen_chunks = 0;        // all-gather chunks whose flag this CTA has already acquired
+      const int prof_empty = prof ? kProfProducerEmptyWait : -1;
       for (int i = cta; i < walk.positions; i += num_ctas) {
         const Tile t = walk.at(i);
         if (!t.valid) continue;
@@ -662,11 +667,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
             const CUtensorMap* bm = (P.passes == 3 && pass == 1) ? &P.tmap_b[1] : &P.tmap_b[0];
             for (int j = j0; j < j1; ++j, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
-              {
-                ProfTimer pt(prof);
-                wait_mbar(bar_empty + 8 * s, ph ^ 1u, timeout_ns, kTimeoutEmptyBar, it);
-                pt.stop(kProfProducerEmptyWait);
-              }
+              wait_mbar(bar_empty + 8 * s, ph ^ 1u, timeout_ns, kTimeoutEmptyBar, it, prof_empty);
               const uint32_t sa = smem_base + s * kStageBytes;
               if constexpr (kCG == 1) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
@@ -690,28 +691,22 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       constexpr uint32_t idesc = make_idesc<kCG, kTf32>();
       uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
       uint32_t s = 0, ph = 0;     // ring position: stage and the phase bit of its current use
+      const uint64_t adesc0 = make_smem_desc(smem_base);
+      const int prof_full = prof ? kProfMmaFullWait : -1, prof_tmem = prof ? kProfMmaTmemWait : -1;
       for (int i = cta; i < walk.positions; i += num_ctas) {
         if (!walk.at(i).valid) continue;
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
           const uint32_t acc = unit & 1u;
-          {
-            ProfTimer pt(prof);
-            wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit);
-            pt.stop(kProfMmaTmemWait);
-          }
+          wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit, prof_tmem);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kBlockN;
           const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
           for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
-            {
-              ProfTimer pt(prof);
-              wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it);
-              pt.stop(kProfMmaFullWait);
-            }
+            wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it, prof_full);
             tc_fence_after();
-            const uint32_t sa = smem_base + s * kStageBytes;
-            const uint64_t adesc = make_smem_desc(sa);
-            const uint64_t bdesc = make_smem_desc(sa + kStageABytes);
+            // stage s sits s * kStageBytes further on: only the address field (16-byte units) moves
+            const uint64_t adesc = adesc0 + s * (kStageBytes >> 4);
+            const uint64_t bdesc = adesc + (kStageABytes >> 4);
 #pragma unroll
             for (int k = 0; k < kBlockKBytes / 32; ++k) {
               // each MMA consumes 32 bytes of K; descriptors advance in 16-byte units
