@@ -19,6 +19,34 @@ thread_local int g_last_cuda_error = 0;
 uint64_t g_timeout_ns = 2000ull * 1000ull * 1000ull;
 int g_profile = 0;
 
+// Tuning knobs for experiments, read from the environment once: EDM_STAGE_LIMIT (ring stages),
+// EDM_BAND (row blocks per band of the tile walk), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
+// shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2).
+struct Tuning {
+  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0;
+  Tuning() {
+    auto get = [](const char* name, int dflt) {
+      const char* e = std::getenv(name);
+      return e ? std::atoi(e) : dflt;
+    };
+    stage_limit = get("EDM_STAGE_LIMIT", 0);
+    band = get("EDM_BAND", 0);
+    push_stride = get("EDM_PUSH_STRIDE", 1);
+    if (push_stride < 1) push_stride = 1;
+    side_streams = get("EDM_SIDE_STREAMS", 2);
+    cta_group = get("EDM_CTA_GROUP", 0);
+  }
+};
+const Tuning& tuning() {
+  static const Tuning t;
+  return t;
+}
+void apply_tuning(LaunchParams& lp) {
+  lp.stage_limit = tuning().stage_limit;
+  lp.band = tuning().band;
+  lp.push_stride = tuning().push_stride;
+}
+
 #define EDM_CUDA(expr)                                   \
   do {                                                   \
     cudaError_t e__ = (expr);                            \
@@ -171,10 +199,7 @@ int max_resident_ctas(int dtype, int cg, int sms, int* out) {
 int pick_cta_group(int dtype, int op, int64_t M, int world) {
   if (dtype != EDM_DTYPE_BF16) return 1;
   int want = M >= 256 ? 2 : 1;
-  if (const char* e = std::getenv("EDM_CTA_GROUP")) {
-    if (e[0] == '1') want = 1;
-    if (e[0] == '2') want = 2;
-  }
+  if (tuning().cta_group == 1 || tuning().cta_group == 2) want = tuning().cta_group;
   if (want == 2 && op == EDM_OP_GEMM_RS && world > 1 && (M / world) % (2 * kBlockM) != 0) want = 1;
   return want;
 }
@@ -266,10 +291,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
-  lp.push_stride = 1;
-  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
-  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
+  apply_tuning(lp);
   return launch_variant(dtype, cg, lp, grid, false, s);
 }
 
@@ -515,8 +537,7 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) 
   const int elem = 2;
   const size_t row_bytes = static_cast<size_t>(P.K) * elem;
   const int64_t chunk_rows = (rows + P.ag_chunks - 1) / P.ag_chunks;
-  int nstreams = 2;
-  if (const char* e = std::getenv("EDM_SIDE_STREAMS")) nstreams = std::atoi(e);
+  int nstreams = tuning().side_streams;
   if (nstreams < 1) nstreams = 1;
   if (nstreams > edm_comm::kSideStreams) nstreams = edm_comm::kSideStreams;
   EDM_CUDA(cudaEventRecord(c->ev_in, stream));
@@ -740,10 +761,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
-  lp.push_stride = 1;
-  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
-  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
+  apply_tuning(lp);
   const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
   if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
   rc = launch_variant(call->dtype, cg, lp, grid, false, s);
@@ -776,10 +794,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   if (lp.ctas_per_vrank < cg) return EDM_ERR_CUDA;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  if (const char* e = std::getenv("EDM_STAGE_LIMIT")) lp.stage_limit = std::atoi(e);
-  lp.push_stride = 1;
-  if (const char* e = std::getenv("EDM_BAND")) lp.band = std::atoi(e);
-  if (const char* e = std::getenv("EDM_PUSH_STRIDE")) lp.push_stride = std::atoi(e) > 0 ? std::atoi(e) : 1;
+  apply_tuning(lp);
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
   rc = launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);

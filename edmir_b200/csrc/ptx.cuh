@@ -68,9 +68,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async_all() {
-  asm volatile("fence.proxy.async;" ::: "memory");
-}
 __device__ __forceinline__ void fence_proxy_async_global() {
   asm volatile("fence.proxy.async.global;" ::: "memory");
 }
@@ -107,23 +104,10 @@ __device__ __forceinline__ void bulk_store(void* dst_global, uint32_t src_smem, 
                "r"(src_smem), "r"(bytes)
                : "memory");
 }
-// Bulk copy global -> shared (local memory), completion in bytes on an mbarrier.
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src_global, uint32_t bytes,
-                                          uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst_smem), "l"(src_global), "r"(bytes), "r"(bar)
-      : "memory");
-}
-// Wait until at most N of this thread's most recent bulk groups are still pending (fully written),
-// or, for the .read form, still reading their shared-memory source.
+// Wait until at most N of this thread's most recent bulk groups are still pending (fully written).
 template <int N>
 __device__ __forceinline__ void bulk_wait_pending() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait_read_pending() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() {
@@ -220,9 +204,6 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 }
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // 16-byte global accesses that bypass L1 (data written by another GPU lands in L2).
 __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {

@@ -37,7 +37,6 @@ constexpr int kPipeBytes = 192 * 1024;  // operand ring: 4 stages of 48 KiB, or 
 constexpr int kThreads = 384;  // 12 warps, see the role list above (registers are granted per 4 warps)
 constexpr int kMaxRanks = 8;
 constexpr int kMaxVirtualRanks = 4;
-constexpr int kCommWarps = 2;
 constexpr int kTmemCols = 512;
 constexpr int kStageABytes = kBlockM * kBlockKBytes;  // 16 KiB
 constexpr int kMaxStages = 6;
@@ -69,6 +68,7 @@ enum ProfSlot : int {
   kProfReducerFlagWait = 8, kProfReducerTotal = 9, kProfPushLoadWait = 10, kProfPushBufferWait = 11,
   kProfPushPublish = 12, kProfPushTotal = 13, kProfKernelTotal = 14, kProfCtas = 15,
   kProfEpiFence = 16, kProfEpiIssue = 17, kProfEpiTmemLoad = 18, kProfPushFence = 19,
+  kProfProducerFlagPoll = 20, kProfProducerProxyFence = 21, kProfEpiTileLoop = 22, kProfEpiFinalNotes = 23,
 };
 __device__ unsigned long long g_prof[24];
 
@@ -198,9 +198,12 @@ struct TileWalk {
   int positions;    // length of the walk (>= total when it has holes)
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
   int band;         // row blocks per band of the walk
+  int rounds;       // RS/AR: rounds of the owner round-robin (= most tiles any rank owns)
+  int defer;        // RS/AR: own tiles of the last `defer` rounds are computed at the very end
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
-  __device__ TileWalk(const RankParams& p, int tile_m, int band_rows) {
+  // units = CTAs (or CTA pairs) walking the tiles concurrently
+  __device__ TileWalk(const RankParams& p, int tile_m, int band_rows, int units) {
     mode = p.mode; rank = p.rank; world = p.world;
     band = band_rows > 0 ? band_rows : 16;  // 16 x 256 rows of A stay in L2 while B streams through once per band
     m_blocks = (p.M + tile_m - 1) / tile_m;
@@ -210,6 +213,11 @@ struct TileWalk {
     mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % tile_m == 0)
                       ? rows_per_rank / tile_m : 0;
     positions = (mode == kAR && world > 1) ? (total + world - 1) / world * world : total;
+    rounds = world > 1 ? positions / world : 0;
+    // about one wave of own tiles goes last: while it is computed nothing has to cross the link
+    // any more, the peers already hold every partial of this rank and reduce during that wave,
+    // and what is left after the last MMA is one local copy and one local reduction
+    defer = min(rounds, units);
   }
 
   // tiles owned by `r`
@@ -239,8 +247,17 @@ struct TileWalk {
       // rank+2, ..., rank.  Pushes therefore leave at a steady rate towards every peer for the
       // whole launch, and every owner receives the partials of its tile R from all ranks at
       // about the same time.
-      const int round = i / world;
-      t.owner = (rank + 1 + (i - round * world)) % world;
+      // The own tiles of the last `defer` rounds are taken out of their rounds and appended.
+      const int full = (rounds - defer) * world;        // positions of the undisturbed rounds
+      const int thin = defer * (world - 1);             // positions of the rounds without own tile
+      int round, d;
+      if (i < full) { round = i / world; d = i - round * world; }
+      else if (i < full + thin) {
+        const int j = i - full;
+        round = rounds - defer + j / (world - 1);
+        d = j - (j / (world - 1)) * (world - 1);        // 0 .. world-2: never this rank
+      } else { round = rounds - defer + (i - full - thin); d = world - 1; }
+      t.owner = (rank + 1 + d) % world;
       t.owned_idx = round;
       t.valid = round < owned_count(t.owner);
       owned_tile(t.owner, round, t.m_blk, t.n_blk);
@@ -367,7 +384,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   constexpr int kColsPerPass = kEpiRowBytes / kOutBytes;   // 128 (bf16) / 64 (fp32)
   constexpr int kPasses = kBlockN / kColsPerPass;          // 2 / 4
   constexpr int kChunksPerPass = kColsPerPass / 32;        // 4 / 2
-  constexpr int kVecPerRow = kEpiRowBytes / 16;            // 16
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
@@ -427,7 +443,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P, kBlockM * kCG, lp.band);
+  const TileWalk walk(P, kBlockM * kCG, lp.band, num_ctas);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -646,7 +662,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                 ProfTimer pa(prof);
                 wait_flag(P.flags[P.rank] + P.gather_flag_off + id, P.epoch,
                           timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
-                pa.stop(20);
+                pa.stop(kProfProducerFlagPoll);
                 if (id < 64) seen_chunks |= 1ull << id;
                 fresh = true;
               }
@@ -655,7 +671,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             if (fresh) {
               ProfTimer pf(prof);
               fence_proxy_async_global();
-              pf.stop(21);
+              pf.stop(kProfProducerProxyFence);
             }
             pt.stop(kProfProducerGatherWait);
           }
@@ -721,7 +737,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         }
       }
     }
-  } else if (warp < 2 + kCommWarps) {
+  } else if (warp < 4) {
     // ============================ all-gather pushes ============================
     if (ag_push) push_shard(warp - 2, &mbox[4 + (warp - 2)]);
     if (fused_reduce) {
@@ -744,6 +760,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     bool bulk_pending = false;  // a bulk copy out of this warp's staging rows may still be reading them
     uint32_t* pend_old = nullptr;  // flags of the (up to two) shipped tiles whose copies may be in flight
     uint32_t* pend_new = nullptr;
+    // a tile of >= 32 K blocks takes longer than a remote copy needs to land (see settle_early use)
+    const bool settle_early = num_kb_pass * P.passes >= 32;
     const bool fused = (P.mode == kRS || P.mode == kAR) && P.world > 1;
     // running fp32 sums of this thread's row: [chunk][row][32 floats], private to the CTA
     float* my_scratch = P.scratch == nullptr ? nullptr
@@ -791,6 +809,15 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         ProfTimer pt(eprof);
         wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter);
         pt.stop(kProfEpiTmemWait);
+        if (settle_early && pend_new != nullptr) {
+          // Long tiles: the previous tile's copies were issued a whole tile time ago and have
+          // landed by now, so its flag can go out one tile (not two) after the data.
+          ProfTimer pw(eprof);
+          bulk_wait_pending<0>();
+          pw.stop(kProfEpiFlagWait);
+          mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_new)), timeout_ns);
+          pend_new = nullptr;
+        }
       }
       __syncwarp();
       tc_fence_after();
@@ -912,13 +939,16 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                    (static_cast<uint32_t>(P.rank) * P.max_owned + slot_idx) * 4 + q;
       }
     }
+    if (eprof) atomicAdd(&g_prof[kProfEpiTileLoop], static_cast<unsigned long long>(globaltimer_ns() - epi_total.t0));
     if (lane == 0) {
+      ProfTimer pfn(eprof);
       if (pend_new != nullptr) {
         bulk_wait_pending<0>();
         if (pend_old != nullptr)
           mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
         mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_new)), timeout_ns);
       }
+      pfn.stop(kProfEpiFinalNotes);
     }
     __syncwarp();
     if (fused_reduce) reduce_units(&mbox[q], false);  // tiles done: help add up the owned tiles

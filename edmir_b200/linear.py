@@ -146,7 +146,8 @@ PROFILE_SLOTS = ("producer_gather_wait", "producer_stage_wait", "mma_operand_wai
                  "epilogue_accumulator_wait", "epilogue_staging_wait", "epilogue_landing_wait", "epilogue_total",
                  "reducer_partial_wait", "reducer_total", "push_load_wait", "push_buffer_wait", "push_publish",
                  "push_total", "kernel_total", "ctas", "epilogue_flag_fence", "epilogue_copy_issue",
-                 "epilogue_accumulator_load", "push_flag_fence", "r20", "r21", "r22", "r23")
+                 "epilogue_accumulator_load", "push_flag_fence", "producer_flag_poll", "producer_proxy_fence",
+                 "epilogue_tile_loop", "epilogue_final_notes")
 
 
 def profile_enable(on: bool = True) -> None:

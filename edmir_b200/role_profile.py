@@ -58,7 +58,7 @@ def main() -> None:
         linear.profile_enable(False)
         ctas = max(prof["ctas"], 1)
         if rank == 0:
-            per = {k: round(v / ctas / 1e3, 1) for k, v in prof.items() if v and k != "ctas" }
+            per = {k: round(v / ctas / 1e3, 1) for k, v in prof.items() if v and k != "ctas" and not k.startswith("reserved") }
             print(f"{label}: {e0.elapsed_time(e1) / args.iters * 1e3:.1f} us/launch  per-CTA us: {per}", flush=True)
 
     for name, op, K, N in LAYER:

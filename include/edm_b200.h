@@ -70,7 +70,9 @@ int edm_status_clear(void);
  * 8 reducer waiting for partial tiles, 9 reducer total, 10 push warps waiting for local loads,
  * 11 push warps waiting for a buffer, 12 push warps publishing chunks, 13 push warps total,
  * 14 kernel total, 15 number of CTAs counted, 16 epilogue flag fences, 17 epilogue copy issue,
- * 18 epilogue accumulator loads, 19 push-warp flag fences, 20-23 reserved.
+ * 18 epilogue accumulator loads, 19 push-warp flag fences, 20 producer polling chunk flags,
+ * 21 producer proxy fences, 22 epilogue tile loop (start to last tile shipped), 23 epilogue waiting
+ * for its last copies.
  * edm_profile_read synchronises the device. */
 int edm_profile_enable(int on);
 int edm_profile_read(uint64_t out[24], int reset);
