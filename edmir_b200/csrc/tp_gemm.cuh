@@ -2,23 +2,31 @@
 // fused into it.  One kernel covers four modes:
 //
 //   PLAIN  D[M,N] = A[M,K] * B[N,K]^T
-//   RS     every rank computes a full partial; the rank that owns a block of rows receives the
-//          other ranks' partial tiles in its symmetric window and adds them in its epilogue
-//          (GEMM + reduce-scatter)
-//   AR     like RS with tile ownership dealt round-robin, then the owner stores the reduced tile
+//   RS     every rank computes a full partial of every tile and ships it -- its own tiles
+//          included -- into the window of the rank that owns the tile's rows; the owner's
+//          reducer warps add the W copies up (GEMM + reduce-scatter)
+//   AR     like RS with tiles dealt round-robin to owners; the owner stores the reduced tile
 //          into every rank's output (GEMM + all-reduce)
-//   AG     two helper warps per CTA push the local row shard of X to every peer while the
-//          tile loop consumes shards as their chunk flags arrive (all-gather + GEMM)
+//   AG     the row shards of X arrive in this rank's gather buffer -- pushed by the peers'
+//          warps or by copy engines -- and the tile loop consumes each shard once its chunk
+//          flags are up (all-gather + GEMM)
 //
 // Both operands are K-major (the reference's "TN" convention, EDM-IR/ir/c-extension/mma.cu:24-25).
-// Roles per CTA (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = peer
-// pushes (AG) or reduction of received partial tiles (RS/AR), warps 4-7 = epilogue (TMEM ->
-// registers -> smem -> global/peer), warp 8 = signaller, warps 9-11 = more reduction (RS/AR).  A system-scope release costs on the
-// order of ten microseconds while remote writes are queued (it drains the SM), so no working
-// warp ever executes one: they post "this data has landed" notes into shared-memory mailboxes
-// and the signaller turns batches of notes into one fence plus relaxed flag stores.
+//
+// Roles per CTA (384 threads = 12 warps):
+//   warp 0      TMA producer (operand ring)
+//   warp 1      MMA issuer (one thread)
+//   warps 2,3   all-gather pushes (sm transport) or reduction of received tiles (RS/AR);
+//               warp 2 also allocates and frees TMEM
+//   warps 4-7   epilogue: TMEM -> registers -> shared-memory staging -> global / peer window
+//   warp 8      signaller
+//   warps 9-11  more pushes / reduction
+// A system-scope release costs on the order of ten microseconds while remote writes are queued
+// (it drains the SM), so no working warp ever executes one: they post "this data has landed"
+// notes into shared-memory mailboxes and the signaller turns batches of notes into one fence plus
+// relaxed flag stores.
 // Accumulators are double buffered in TMEM (2 x 256 columns) so the epilogue of tile i, which
-// is where the NVLink stores happen, overlaps the MMAs of tile i+1.
+// is where the NVLink traffic is issued, overlaps the MMAs of tile i+1.
 //
 // Every wait (mbarrier or peer flag) is bounded: on expiry the kernel records a status code and
 // all remaining waits fall through, so the launch always terminates and frees its TMEM.
