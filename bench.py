@@ -42,6 +42,7 @@ LAYER_OPS = (
     ("down", "gemm_rs", FFN // TP_REF, HIDDEN),
 )
 NVLINK_GBS_NOMINAL = 900.0
+JSON_OUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch (gate_up, 55 % of the layer's
 # flops), from the ncu capture summarised in profiles/tp_gemm_bf16_layer_1gpu.md
@@ -167,7 +168,7 @@ def run_reference(args) -> None:
         "e2e": {"value": value, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=JSON_OUT, flush=True)
 
 
 def workload_config(M: int, world: int) -> dict:
@@ -352,7 +353,7 @@ def run_ours(args) -> None:
             v, desc = cpu_layer_us(M, min(M, 1024), threads)
             line["cpu_baseline"] = {"value": round(v, 1), "unit": "us/layer", "cores": threads, "kind": "port",
                                     "sample": desc, "selector_sweep_us": round(selector_sweep_us(), 1)}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=JSON_OUT, flush=True)
 
     if ctx is not None:
         sync_all()
@@ -361,7 +362,18 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def _claim_stdout():
+    """Keep stdout for the one JSON line: everything else that writes to file descriptor 1
+    (library banners such as NCCL's version line) is sent to stderr."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(saved, "w")
+
+
 def main() -> None:
+    global JSON_OUT
+    JSON_OUT = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
