@@ -21,9 +21,10 @@ int g_profile = 0;
 
 // Tuning knobs for experiments, read from the environment once: EDM_STAGE_LIMIT (ring stages),
 // EDM_BAND (row blocks per band of the tile walk), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
-// shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2).
+// shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2),
+// EDM_BLOCK_N (32 or 256: tile width of the single-CTA plain GEMM).
 struct Tuning {
-  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0;
+  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0;
   Tuning() {
     auto get = [](const char* name, int dflt) {
       const char* e = std::getenv(name);
@@ -35,6 +36,7 @@ struct Tuning {
     if (push_stride < 1) push_stride = 1;
     side_streams = get("EDM_SIDE_STREAMS", 2);
     cta_group = get("EDM_CTA_GROUP", 0);
+    block_n = get("EDM_BLOCK_N", 0);
   }
 };
 const Tuning& tuning() {
@@ -90,8 +92,24 @@ WriteValue32Fn write_value_fn() {
 }
 
 // K-major matrix [rows, k] with leading dimension ld (elements); box = 128 bytes of K x box_rows.
+// Encoding is a pure function of its arguments, so the last few results are kept: a decode-sized
+// launch is short enough for two driver calls per operand to show.
+struct TmapKey {
+  const void* base; int64_t rows, k, ld; int elem_bytes, box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && k == o.k && ld == o.ld && elem_bytes == o.elem_bytes &&
+           box_rows == o.box_rows;
+  }
+};
 int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int64_t ld, int elem_bytes,
               int box_rows) {
+  constexpr int kCache = 16;
+  thread_local TmapKey keys[kCache] = {};
+  thread_local CUtensorMap maps[kCache];
+  thread_local int next = 0;
+  const TmapKey key{base, rows, k, ld, elem_bytes, box_rows};
+  for (int i = 0; i < kCache; ++i)
+    if (keys[i].base != nullptr && keys[i] == key) { *m = maps[i]; return EDM_OK; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return EDM_ERR_CUDA;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * elem_bytes) & 15)) return EDM_ERR_BAD_ARG;
@@ -108,6 +126,9 @@ int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int64_t
     g_last_cuda_error = 100000 + static_cast<int>(r);
     return EDM_ERR_CUDA;
   }
+  keys[next] = key;
+  maps[next] = *m;
+  next = (next + 1) % kCache;
   return EDM_OK;
 }
 
@@ -120,9 +141,9 @@ int num_sms() {
 
 // One launch path for every variant: plain, cooperative (emulated ranks must be co-resident),
 // and/or as clusters of 2 (CTA pairs).
-template <int kCG, bool kTf32, typename OutT>
+template <int kCG, int kBN, bool kTf32, typename OutT>
 struct Variant {
-  static void* fn() { return reinterpret_cast<void*>(&tp_gemm_kernel<kCG, kTf32, OutT>); }
+  static void* fn() { return reinterpret_cast<void*>(&tp_gemm_kernel<kCG, kBN, kTf32, OutT>); }
   static int configure() {
     static bool done = false;
     if (!done) {
@@ -181,16 +202,26 @@ struct Variant {
   }
 };
 
-int launch_variant(int dtype, int cg, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
+int launch_variant(int dtype, int cg, int bn, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
   if (dtype == EDM_DTYPE_BF16) {
-    if (cg == 2) return Variant<2, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
-    return Variant<1, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
+    if (cg == 2) return Variant<2, 256, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
+    if (bn == 32) return Variant<1, 32, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
+    return Variant<1, 256, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
   }
-  return Variant<1, true, float>::launch(lp, grid, coop, stream);
+  return Variant<1, 256, true, float>::launch(lp, grid, coop, stream);
+}
+
+// Tile width of the plain bf16 GEMM.  With a single row block (M <= 128: decode) the job is to
+// stream the weights once, so 128x32 tiles spread N over all SMs; otherwise 256 wide.
+int pick_block_n(int dtype, int cg, int64_t M, int64_t N, int sms) {
+  if (dtype != EDM_DTYPE_BF16 || cg != 1) return kBlockN;
+  if (tuning().block_n == 32 || tuning().block_n == 256) return tuning().block_n;
+  const int64_t wide_tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
+  return (M <= kBlockM && wide_tiles * 2 <= sms) ? 32 : kBlockN;
 }
 
 int max_resident_ctas(int dtype, int cg, int sms, int* out) {
-  if (dtype == EDM_DTYPE_BF16 && cg == 2) return Variant<2, false, __nv_bfloat16>::max_resident(sms, out);
+  if (dtype == EDM_DTYPE_BF16 && cg == 2) return Variant<2, 256, false, __nv_bfloat16>::max_resident(sms, out);
   *out = sms;
   return EDM_OK;
 }
@@ -217,8 +248,8 @@ size_t split_ws_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 // Fills tmap_a/tmap_b (and runs the tf32 split for fp32) for a GEMM A[M,K] x B[N,K].
-// `cg` = CTAs sharing a tile: each loads kBlockN / cg rows of the B tile per stage.
-int prepare_operands(RankParams& P, int dtype, int cg, const void* a, int64_t lda, int64_t a_rows,
+// `cg` = CTAs sharing a tile of width `bn`: each loads bn / cg rows of the B tile per stage.
+int prepare_operands(RankParams& P, int dtype, int cg, int bn, const void* a, int64_t lda, int64_t a_rows,
                      const void* b, int64_t ldb, int64_t N, int64_t K, void* ws, size_t ws_bytes,
                      cudaStream_t stream) {
   if (dtype == EDM_DTYPE_BF16) {
@@ -226,7 +257,7 @@ int prepare_operands(RankParams& P, int dtype, int cg, const void* a, int64_t ld
     int rc = make_tmap(&P.tmap_a[0], a, a_rows, K, lda, 2, kBlockM);
     if (rc) return rc;
     P.tmap_a[1] = P.tmap_a[0];
-    rc = make_tmap(&P.tmap_b[0], b, N, K, ldb, 2, kBlockN / cg);
+    rc = make_tmap(&P.tmap_b[0], b, N, K, ldb, 2, bn / cg);
     if (rc) return rc;
     P.tmap_b[1] = P.tmap_b[0];
     P.passes = 1;
@@ -249,8 +280,8 @@ int prepare_operands(RankParams& P, int dtype, int cg, const void* a, int64_t ld
   int rc;
   if ((rc = make_tmap(&P.tmap_a[0], a_hi, a_rows, K, K, 4, kBlockM))) return rc;
   if ((rc = make_tmap(&P.tmap_a[1], a_lo, a_rows, K, K, 4, kBlockM))) return rc;
-  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, kBlockN / cg))) return rc;
-  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, kBlockN / cg))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[0], b_hi, N, K, K, 4, bn / cg))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[1], b_lo, N, K, K, 4, bn / cg))) return rc;
   P.passes = 3;
   P.seg_kblocks = kSegKBlocks;
   P.scratch = reinterpret_cast<float*>(w + 2 * a_sz + 2 * b_sz);
@@ -276,23 +307,24 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   RankParams& P = lp.r[0];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int cg = pick_cta_group(dtype, EDM_OP_GEMM, M, 1);
-  rc = prepare_operands(P, dtype, cg, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  const int bn = pick_block_n(dtype, cg, M, N, sms);
+  rc = prepare_operands(P, dtype, cg, bn, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
   if (rc) return rc;
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
   P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
   P.out = d; P.ld_out = ldd;
-  const int sms = num_sms();
-  if (sms <= 0) return EDM_ERR_CUDA;
   int resident = 0;
   if ((rc = max_resident_ctas(dtype, cg, sms, &resident))) return rc;
-  const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + kBlockN - 1) / kBlockN));
+  const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + bn - 1) / bn));
   const int grid = tiles * cg < resident ? tiles * cg : resident;
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   apply_tuning(lp);
-  return launch_variant(dtype, cg, lp, grid, false, s);
+  return launch_variant(dtype, cg, bn, lp, grid, false, s);
 }
 
 }  // namespace
@@ -363,7 +395,7 @@ extern "C" int edm_gemm_fp32_static(const void* a, int64_t lda, const void* b, i
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
-  return launch_variant(EDM_DTYPE_FP32, 1, lp, grid, false, s);
+  return launch_variant(EDM_DTYPE_FP32, 1, kBlockN, lp, grid, false, s);
 }
 
 // ======================================================================== contexts
@@ -463,7 +495,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     if (call.op == EDM_OP_GEMM_AR || call.op == EDM_OP_GEMM_RS || call.op == EDM_OP_GEMM ||
         call.op == EDM_OP_AG_GEMM) {
       P.mode = kPlain; P.epoch = 1;
-      return prepare_operands(P, call.dtype, cg, call.a, call.lda, call.M, call.b, call.ldb, call.N,
+      return prepare_operands(P, call.dtype, cg, kBlockN, call.a, call.lda, call.M, call.b, call.ldb, call.N,
                               call.K, call.workspace, call.workspace_bytes, stream);
     }
     return EDM_ERR_BAD_ARG;
@@ -515,7 +547,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
       const size_t off = static_cast<size_t>(d - c->base[c->rank]);
       for (int p = 0; p < W; ++p) P.peer_out[p] = c->base[p] + off;
     }
-    rc = prepare_operands(P, call.dtype, cg, call.a, call.lda, call.M, call.b, call.ldb, call.N, call.K,
+    rc = prepare_operands(P, call.dtype, cg, kBlockN, call.a, call.lda, call.M, call.b, call.ldb, call.N, call.K,
                           call.workspace, call.workspace_bytes, stream);
     if (rc) return rc;
   }
@@ -764,7 +796,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   apply_tuning(lp);
   const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
   if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
-  rc = launch_variant(call->dtype, cg, lp, grid, false, s);
+  rc = launch_variant(call->dtype, cg, kBlockN, lp, grid, false, s);
   if (rc) return rc;
   if (ce) return ag_copy_engine_after_launch(comm, s);
   return EDM_OK;
@@ -797,7 +829,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   apply_tuning(lp);
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
-  rc = launch_variant(calls[0].dtype, cg, lp, lp.ctas_per_vrank * n, true, s);
+  rc = launch_variant(calls[0].dtype, cg, kBlockN, lp, lp.ctas_per_vrank * n, true, s);
   if (rc) return rc;
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_after_launch(comms[i], s))) return rc;

@@ -39,7 +39,7 @@
 namespace edm {
 
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
+constexpr int kBlockN = 256;  // widest tile (the TMEM double buffer holds 2 x 256 columns); a 32-wide variant serves tiny M
 constexpr int kBlockKBytes = 128;  // one 128B swizzle row of K per stage
 constexpr int kPipeBytes = 192 * 1024;  // operand ring: 4 stages of 48 KiB, or 6 of 32 KiB for CTA pairs
 constexpr int kThreads = 384;  // 12 warps, see the role list above (registers are granted per 4 warps)
@@ -47,7 +47,7 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxVirtualRanks = 4;
 constexpr int kTmemCols = 512;
 constexpr int kStageABytes = kBlockM * kBlockKBytes;  // 16 KiB
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 9;
 constexpr int kEpiRowBytes = 256;                      // staging row per pass
 constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;       // 8 KiB per epilogue warp
 constexpr int kSmemBytes = kPipeBytes + 4 * kEpiWarpBytes + 1024 /*align*/ + 256;
@@ -211,11 +211,11 @@ struct TileWalk {
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
   // units = CTAs (or CTA pairs) walking the tiles concurrently
-  __device__ TileWalk(const RankParams& p, int tile_m, int band_rows, int units) {
+  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units) {
     mode = p.mode; rank = p.rank; world = p.world;
     band = band_rows > 0 ? band_rows : 16;  // 16 x 256 rows of A stay in L2 while B streams through once per band
     m_blocks = (p.M + tile_m - 1) / tile_m;
-    n_blocks = (p.N + kBlockN - 1) / kBlockN;
+    n_blocks = (p.N + tile_n - 1) / tile_n;
     total = m_blocks * n_blocks;
     const int rows_per_rank = p.M / max(world, 1);
     mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % tile_m == 0)
@@ -297,12 +297,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
   return d;
 }
-template <int kCG, bool kTf32>
+template <int kCG, int kBN, bool kTf32>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   const uint32_t fmt = kTf32 ? 2u : 1u;  // 1 = BF16, 2 = TF32
   return (1u << 4)                        // D format F32
          | (fmt << 7) | (fmt << 10)       // A, B formats; both K-major (bits 15,16 = 0)
-         | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>((kBlockM * kCG) >> 4) << 24);
+         | (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>((kBlockM * kCG) >> 4) << 24);
 }
 
 template <int V> struct IntTag { static constexpr int value = V; };
@@ -378,20 +378,25 @@ template <> struct OutPack<float> {
 // each CTA loads its 128 rows of A and its 128-row half of the B tile, the even CTA issues
 // cta_group::2 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its own
 // 128 accumulator rows, so the epilogue is the same per-CTA code in both variants.
-template <int kCG, bool kTf32, typename OutT>
+// kBN = tile width: 256, or 32 for decode-sized M (one row block): 128x32 tiles give every SM a
+// slab of the weights to stream instead of leaving most SMs idle (plain GEMM only).  Such a launch
+// is bound by the issue cost of its K/16 MMA instructions per CTA, not by memory; splitting K
+// over CTAs would be the next step for those shapes.
+template <int kCG, int kBN, bool kTf32, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
-  constexpr int kStageBBytes = (kBlockN / kCG) * kBlockKBytes;  // 32 KiB, or 16 KiB per CTA of a pair
+  static_assert(kBN == 256 || (kBN == 32 && kCG == 1), "tile width");
+  constexpr int kStageBBytes = (kBN / kCG) * kBlockKBytes;  // 32 KiB, 16 KiB per CTA of a pair, or 4 KiB
   constexpr int kStageBytes = kStageABytes + kStageBBytes;
-  constexpr int kStages = kPipeBytes / kStageBytes;             // 4 or 6
+  constexpr int kStages = kPipeBytes / kStageBytes;             // 4, 6 or 9
   static_assert(kStages <= kMaxStages, "barrier array too small");
   constexpr int kElemBytes = kTf32 ? 4 : 2;
   constexpr int kBlockK = kBlockKBytes / kElemBytes;   // elements of K per stage
   constexpr int kOutBytes = sizeof(OutT);
-  constexpr int kTileOutBytes = kBlockM * kBlockN * kOutBytes;
+  constexpr int kTileOutBytes = kBlockM * kBN * kOutBytes;
   constexpr int kColsPerPass = kEpiRowBytes / kOutBytes;   // 128 (bf16) / 64 (fp32)
-  constexpr int kPasses = kBlockN / kColsPerPass;          // 2 / 4
-  constexpr int kChunksPerPass = kColsPerPass / 32;        // 4 / 2
+  constexpr int kPasses = kBN >= kColsPerPass ? kBN / kColsPerPass : 1;               // 2 / 4 (1 for the narrow tile)
+  constexpr int kChunksPerPass = (kBN >= kColsPerPass ? kColsPerPass : kBN) / 32;     // 4 / 2 (1)
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
@@ -451,7 +456,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P, kBlockM * kCG, lp.band, num_ctas);
+  const TileWalk walk(P, kBlockM * kCG, kBN, lp.band, num_ctas);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -543,8 +548,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       const int idx = item / kCG, hp = item - idx * kCG;  // owned tile, half within the pair tile
       int m_blk, n_blk;
       walk.owned_tile(P.rank, idx, m_blk, n_blk);
-      const int m0 = (m_blk * kCG + hp) * kBlockM, n0 = n_blk * kBlockN;
-      const int valid_rows = min(kBlockM, P.M - m0), valid_cols = min(kBlockN, P.N - n0);
+      const int m0 = (m_blk * kCG + hp) * kBlockM, n0 = n_blk * kBN;
+      const int valid_rows = min(kBlockM, P.M - m0), valid_cols = min(kBN, P.N - n0);
       const int64_t out_row0 = P.mode == kRS ? m0 - P.rank * rows_per_rank : m0;
       const int64_t ld_bytes = P.ld_out * kOutBytes;
       const char* slot0 = P.win[P.rank] + static_cast<int64_t>(item) * kTileOutBytes;
@@ -647,7 +652,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         const Tile t = walk.at(i);
         if (!t.valid) continue;
         const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM;  // this CTA's rows of A
-        const int n0 = t.n_blk * kBlockN + static_cast<int>(pr) * (kBlockN / kCG);  // its rows of B
+        const int n0 = t.n_blk * kBN + static_cast<int>(pr) * (kBN / kCG);  // its rows of B
         const CUtensorMap* amap = &P.tmap_a[0];
         int a_row = m0;
         if (P.mode == kAG) {
@@ -712,7 +717,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   } else if (warp == 1) {
     // ============================ MMA issuer ============================
     if (lane == 0 && pr == 0) {
-      constexpr uint32_t idesc = make_idesc<kCG, kTf32>();
+      constexpr uint32_t idesc = make_idesc<kCG, kBN, kTf32>();
       uint32_t it = 0, unit = 0;  // unit = (tile, K segment): one TMEM accumulator each
       uint32_t s = 0, ph = 0;     // ring position: stage and the phase bit of its current use
       const uint64_t adesc0 = make_smem_desc(smem_base);
@@ -723,7 +728,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           const uint32_t acc = unit & 1u;
           wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit, prof_tmem);
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * kBlockN;
+          const uint32_t d_tmem = tmem_base + acc * kBN;
           const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
           for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
             wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it, prof_full);
@@ -786,9 +791,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           wait_mbar(bar_tfull + 8 * sacc, (unit >> 1) & 1u, timeout_ns, kTimeoutTmemFull, unit);
         __syncwarp();
         tc_fence_after();
-        const uint32_t staddr = tmem_base + sacc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t staddr = tmem_base + sacc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < kBlockN / 32; ++c) {
+        for (int c = 0; c < kBN / 32; ++c) {
           uint32_t raw[32];
           tmem_ld_32x32(staddr + c * 32, raw);
           tmem_ld_wait();
@@ -833,8 +838,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       // Where the tile goes.  Fused modes: every tile -- this rank's own included -- is shipped
       // as a partial into the owner's window slot [source rank][slot]; the owner's reducer warps
       // add the slots up.  Otherwise it is written to the output in place.
-      const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBlockN;
-      const int valid_cols = min(kBlockN, P.N - n0);
+      const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBN;
+      const int valid_cols = min(kBN, P.N - n0);
       const int valid_rows = min(kBlockM, P.M - m0);
       char* dst_base;
       if (fused)
@@ -843,7 +848,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         dst_base = static_cast<char*>(P.out) + (static_cast<int64_t>(m0) * P.ld_out + n0) * kOutBytes;
       const int64_t dst_ld = P.ld_out * kOutBytes;
 
-      const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int h = 0; h < kPasses; ++h) {
 #pragma unroll
@@ -854,7 +859,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           tmem_ld_32x32(taddr + c * 32, raw);
           tmem_ld_wait();
           ptl.stop(kProfEpiTmemLoad);
-          if (c == kBlockN / 32 - 1) {
+          if (c == kBN / 32 - 1) {
             // accumulator fully read: hand the TMEM buffer back to the MMA warp
             tc_fence_before();
             __syncwarp();

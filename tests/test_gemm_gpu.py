@@ -26,6 +26,7 @@ def _rand(shape, scale, dtype, seed):
     (128, 256, 64), (128, 256, 512), (256, 512, 128),      # whole tiles
     (1, 4096, 1792), (16, 4096, 1792), (128, 4096, 1792),  # decode-sized rows
     (1000, 768, 520), (130, 264, 72), (8, 8, 8),           # ragged M, N, K edges
+    (5, 1000, 264), (128, 40, 4096),                       # narrow (128x32) tiles with a ragged last tile
     (1024, 4096, 3584),
 ])
 def test_gemm_bf16_matches_oracle(cuda_clean, M, N, K):
