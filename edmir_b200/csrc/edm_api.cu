@@ -757,6 +757,27 @@ int edm_comm_heap_reset(edm_comm_t* c) {
 int edm_comm_rank(const edm_comm_t* c) { return c ? c->rank : -1; }
 int edm_comm_world(const edm_comm_t* c) { return c ? c->world : -1; }
 
+int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m, int tile_n, int band_rows,
+                  int units, int32_t* out, int64_t capacity, int64_t* positions) {
+  if (op < EDM_OP_GEMM || op > EDM_OP_AG_GEMM || world < 1 || world > 8 || rank < 0 || rank >= world || M <= 0 ||
+      N <= 0 || M > INT32_MAX || N > INT32_MAX || tile_m <= 0 || tile_n <= 0 || units < 1 || !positions)
+    return EDM_ERR_BAD_ARG;
+  const int mode = op == EDM_OP_GEMM ? kPlain : op == EDM_OP_GEMM_RS ? kRS : op == EDM_OP_GEMM_AR ? kAR : kAG;
+  const TileWalk walk(mode, rank, world, static_cast<int>(M), static_cast<int>(N), tile_m, tile_n, band_rows, units);
+  if (mode == kRS && world > 1 && walk.mb_per_rank == 0) return EDM_ERR_UNSUPPORTED;
+  *positions = walk.positions;
+  if (!out) return EDM_OK;
+  if (capacity < walk.positions) return EDM_ERR_CAPACITY;
+  for (int i = 0; i < walk.positions; ++i) {
+    const Tile t = walk.at(i);
+    out[4 * i + 0] = t.valid ? t.m_blk : -1;
+    out[4 * i + 1] = t.valid ? t.n_blk : -1;
+    out[4 * i + 2] = t.owner;
+    out[4 * i + 3] = t.owned_idx;
+  }
+  return EDM_OK;
+}
+
 int edm_comm_p2p_probe(edm_comm_t* c, int peer, size_t bytes, int mode, void* stream) {
   if (!c || peer < 0 || peer >= c->world || !c->base[peer] || (mode != 0 && mode != 1)) return EDM_ERR_BAD_ARG;
   if (bytes == 0 || bytes % 8192 || bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;

@@ -190,7 +190,7 @@ struct Tile {
 
 // Walk an (mb x nb) grid in bands of kBand row-blocks so that concurrently running CTAs share
 // A and B panels in L2 (taller bands re-read B less often; 16 measured best on the layer's shapes).
-__device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n, int kBand = 8) {
+__host__ __device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n, int kBand = 8) {
   const int per_band = kBand * nb;
   const int band = i / per_band;
   const int first = band * kBand;
@@ -206,20 +206,33 @@ struct TileWalk {
   int positions;    // length of the walk (>= total when it has holes)
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
   int band;         // row blocks per band of the walk
+  int ag_head_blocks, ag_head_band;  // all-gather: the first row blocks are walked in lower bands
   int rounds;       // RS/AR: rounds of the owner round-robin (= most tiles any rank owns)
   int defer;        // RS/AR: own tiles of the last `defer` rounds are computed at the very end
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
   // units = CTAs (or CTA pairs) walking the tiles concurrently
-  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units) {
-    mode = p.mode; rank = p.rank; world = p.world;
+  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units)
+      : TileWalk(p.mode, p.rank, p.world, p.M, p.N, tile_m, tile_n, band_rows, units) {}
+  __host__ __device__ TileWalk(int mode_, int rank_, int world_, int M, int N, int tile_m, int tile_n,
+                               int band_rows, int units) {
+    mode = mode_; rank = rank_; world = world_;
     band = band_rows > 0 ? band_rows : 16;  // 16 x 256 rows of A stay in L2 while B streams through once per band
-    m_blocks = (p.M + tile_m - 1) / tile_m;
-    n_blocks = (p.N + tile_n - 1) / tile_n;
+    m_blocks = (M + tile_m - 1) / tile_m;
+    n_blocks = (N + tile_n - 1) / tile_n;
     total = m_blocks * n_blocks;
-    const int rows_per_rank = p.M / max(world, 1);
-    mb_per_rank = (world > 1 && rows_per_rank * world == p.M && rows_per_rank % tile_m == 0)
+    const int rows_per_rank = M / max(world, 1);
+    mb_per_rank = (world > 1 && rows_per_rank * world == M && rows_per_rank % tile_m == 0)
                       ? rows_per_rank / tile_m : 0;
+    // all-gather: shards arrive one after the other, about twice as fast as they are consumed.
+    // A band must not reach further ahead than what has arrived when its first wave starts: two
+    // shards per band over the first four shards, then the full band height.
+    ag_head_blocks = 0;
+    ag_head_band = band;
+    if (mode == kAG && mb_per_rank > 0 && band_rows <= 0 && 2 * mb_per_rank < band) {
+      ag_head_blocks = min(m_blocks, 4 * mb_per_rank);
+      ag_head_band = 2 * mb_per_rank;
+    }
     positions = (mode == kAR && world > 1) ? (total + world - 1) / world * world : total;
     rounds = world > 1 ? positions / world : 0;
     // about one wave of own tiles goes last: while it is computed nothing has to cross the link
@@ -229,13 +242,13 @@ struct TileWalk {
   }
 
   // tiles owned by `r`
-  __device__ int owned_count(int r) const {
+  __host__ __device__ int owned_count(int r) const {
     if (mode == kRS) return mb_per_rank * n_blocks;
     if (mode == kAR && world > 1) return (total - r + world - 1) / world;
     return total;
   }
   // coordinates of the idx-th tile owned by `r`
-  __device__ void owned_tile(int r, int idx, int& m_blk, int& n_blk) const {
+  __host__ __device__ void owned_tile(int r, int idx, int& m_blk, int& n_blk) const {
     if (mode == kRS) {
       int lm;
       band_order(idx, mb_per_rank, n_blocks, lm, n_blk, band);
@@ -247,7 +260,7 @@ struct TileWalk {
     }
   }
 
-  __device__ Tile at(int i) const {
+  __host__ __device__ Tile at(int i) const {
     Tile t;
     t.valid = true;
     if ((mode == kRS || mode == kAR) && world > 1) {
@@ -271,7 +284,13 @@ struct TileWalk {
       owned_tile(t.owner, round, t.m_blk, t.n_blk);
     } else if (mode == kAG && mb_per_rank > 0) {
       int pm, n;
-      band_order(i, m_blocks, n_blocks, pm, n, band);
+      const int head_tiles = ag_head_blocks * n_blocks;
+      if (i < head_tiles) {
+        band_order(i, ag_head_blocks, n_blocks, pm, n, ag_head_band);
+      } else {
+        band_order(i - head_tiles, m_blocks - ag_head_blocks, n_blocks, pm, n, band);
+        pm += ag_head_blocks;
+      }
       t.m_blk = (rank * mb_per_rank + pm) % m_blocks;  // own shard first, then rank+1, ...
       t.n_blk = n;
       t.owner = rank;

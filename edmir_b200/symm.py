@@ -190,3 +190,19 @@ class EmulatedGroup:
     def close(self) -> None:
         for ctx in self.ranks:
             ctx.close()
+
+
+def tile_walk(op: str, rank: int, world: int, M: int, N: int, tile_m: int = 256, tile_n: int = 256,
+              band_rows: int = 0, units: int = 74) -> list[tuple[int, int, int, int]]:
+    """Order in which rank ``rank`` computes the output tiles of an ``[M, N]`` launch, as
+    ``(row_block, col_block, owner, index_among_owner's_tiles)``; holes of the all-reduce walk
+    have row and column -1.  Evaluated on the host by the same code the kernel runs."""
+    lib = _lib.load()
+    code = _lib.EDM_OP_GEMM if op == "gemm" else _OPS[op]
+    n = C.c_int64()
+    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, units, None, 0, C.byref(n)),
+               "edm_tile_walk")
+    buf = (C.c_int32 * (4 * n.value))()
+    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, units, buf, n.value,
+                                 C.byref(n)), "edm_tile_walk")
+    return [tuple(buf[4 * i:4 * i + 4]) for i in range(n.value)]

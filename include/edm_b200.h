@@ -133,6 +133,17 @@ int edm_comm_heap_reset(edm_comm_t* comm);
  * figures feed the selector's transfer term ("calibrated from ... P2P tests",
  * paper/mlsys-2027/model.md:111).  Both ranks of a pair may probe each other at once. */
 int edm_comm_p2p_probe(edm_comm_t* comm, int peer, size_t bytes, int mode, void* stream);
+/* The order in which one rank's CTAs take the output tiles of a launch (host-side evaluation of
+ * the enumeration the kernel uses; no device work).  tile_m is 128, or 256 when a CTA pair shares
+ * a tile; tile_n 256 (32 for decode-sized plain GEMMs); band_rows 0 = default; units = CTAs (or
+ * pairs) of the launch.  Writes *positions = length of the walk and, when `out` is not NULL and
+ * holds `capacity` >= *positions entries, four int32 per position: row block, column block (both
+ * -1 for a hole of the all-reduce walk), owner rank, index among the owner's tiles.  No
+ * reference counterpart (the reference has no multi-tile launch, ir/c-extension/mma.cu:168-176);
+ * used by the CPU tests to check that every tile is produced exactly once per rank and that all
+ * ranks agree on owners and slots. */
+int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m, int tile_n, int band_rows,
+                  int units, int32_t* out, int64_t capacity, int64_t* positions);
 int edm_comm_rank(const edm_comm_t* comm);
 int edm_comm_world(const edm_comm_t* comm);
 

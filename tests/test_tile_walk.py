@@ -1,0 +1,97 @@
+"""The tile enumeration of the fused launches, evaluated on the host through the C ABI.
+
+Every rank's CTAs take output tiles in the order ``edm_tile_walk`` reports.  The protocol relies
+on three properties, checked here for every mode, world size and a set of ragged shapes:
+each rank produces every tile exactly once; all ranks agree on which rank owns a tile and on the
+slot (index among the owner's tiles) its partials land in; and slots of one owner are distinct.
+"""
+import itertools
+
+import pytest
+
+from edmir_b200 import symm
+
+SHAPES = [(8192, 8192), (8192, 1280), (2048, 7168), (1024, 256), (4096, 300), (1536, 2304), (256, 256)]
+
+
+def _blocks(M, N, tile_m, tile_n):
+    return -(-M // tile_m), -(-N // tile_n)
+
+
+@pytest.mark.parametrize("tile_m", [128, 256])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("op", ["gemm", "gemm_rs", "gemm_ar", "ag_gemm"])
+def test_every_tile_once_and_ranks_agree(native_lib, op, world, tile_m):
+    for (M, N), band, units in itertools.product(SHAPES, (0, 8), (1, 37, 148)):
+        if op == "gemm" and world > 1:
+            continue
+        if op == "gemm_rs" and (M % world or (M // world) % tile_m):
+            continue
+        mb, nb = _blocks(M, N, tile_m, 256)
+        owners: dict = {}
+        for rank in range(world):
+            walk = symm.tile_walk(op, rank, world, M, N, tile_m, 256, band, units)
+            tiles = [(m, n) for m, n, _, _ in walk if m >= 0]
+            assert sorted(tiles) == sorted(itertools.product(range(mb), range(nb))), (op, world, M, N, rank)
+            if op == "gemm_ar" and world > 1:
+                assert len(walk) % world == 0 and len(walk) - len(tiles) < world
+            else:
+                assert len(walk) == len(tiles)
+            for m, n, owner, idx in walk:
+                if m < 0:
+                    continue
+                if op in ("gemm_rs", "gemm_ar") and world > 1:
+                    assert owners.setdefault((m, n), (owner, idx)) == (owner, idx)
+                else:
+                    assert owner == rank
+        if owners:
+            per_owner: dict = {}
+            for (m, n), (owner, idx) in owners.items():
+                per_owner.setdefault(owner, []).append(idx)
+                if op == "gemm_rs":
+                    assert owner == m // (mb // world)
+            for owner, idxs in per_owner.items():
+                assert sorted(idxs) == list(range(len(idxs))), (op, world, M, N, owner)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_walk_sends_to_every_peer_each_round_and_ends_on_own_tiles(native_lib, world):
+    M, N, units = 8192, 8192, 74
+    for op in ("gemm_rs", "gemm_ar"):
+        for rank in range(world):
+            walk = symm.tile_walk(op, rank, world, M, N, 256, 256, 0, units)
+            rounds = len(walk) // world
+            defer = min(rounds, units)
+            head = walk[:(rounds - defer) * world]
+            for r in range(rounds - defer):
+                assert [o for _, _, o, _ in head[r * world:(r + 1) * world]] == \
+                    [(rank + 1 + d) % world for d in range(world)]
+            tail = walk[-defer:]
+            assert all(o == rank for _, _, o, _ in tail)
+            middle = walk[(rounds - defer) * world:len(walk) - defer]
+            assert all(o != rank for _, _, o, _ in middle)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_gather_walk_follows_arrival_order(native_lib, world):
+    M, N, tile_m = 8192, 7168, 256
+    per_rank = M // world // tile_m
+    for rank in range(world):
+        walk = symm.tile_walk("ag_gemm", rank, world, M, N, tile_m, 256, 0, 74)
+        shard_of = [((m - rank * per_rank) % (M // tile_m)) // per_rank for m, _, _, _ in walk]
+        assert all(s == 0 for s in shard_of[:min(per_rank, 16)])      # first tiles: own rows
+        # position of the first tile of shard s (in arrival order s = 0 own, 1 = rank+1, ...)
+        first = {s: shard_of.index(s) for s in range(world)}
+        assert [first[s] for s in range(world)] == sorted(first.values())
+        # over the first four shards a shard is started only when the shard two places earlier
+        # (which arrived two transfers earlier) is finished
+        last = {s: len(shard_of) - 1 - shard_of[::-1].index(s) for s in range(world)}
+        for s in range(2, min(world, 4)):
+            assert first[s] > last[s - 2]
+
+
+def test_bad_arguments(native_lib):
+    with pytest.raises(ValueError):
+        symm.tile_walk("gemm_rs", 2, 2, 1024, 1024)
+    with pytest.raises(ValueError):
+        symm.tile_walk("gemm_rs", 0, 2, 1024 + 128, 1024)   # rows per rank not on tile edges
