@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -22,9 +23,10 @@ int g_profile = 0;
 // Tuning knobs for experiments, read from the environment once: EDM_STAGE_LIMIT (ring stages),
 // EDM_BAND (row blocks per band of the tile walk), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
 // shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2),
-// EDM_BLOCK_N (32 or 256: tile width of the single-CTA plain GEMM).
+// EDM_BLOCK_N (32 or 256: tile width of the single-CTA plain GEMM), EDM_TAIL_SPLIT (most pieces a
+// tile of an incomplete last wave is cut into along K; 0 or 1: none).
 struct Tuning {
-  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0;
+  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0, tail_split = kTailMaxParts;
   Tuning() {
     auto get = [](const char* name, int dflt) {
       const char* e = std::getenv(name);
@@ -37,6 +39,7 @@ struct Tuning {
     side_streams = get("EDM_SIDE_STREAMS", 2);
     cta_group = get("EDM_CTA_GROUP", 0);
     block_n = get("EDM_BLOCK_N", 0);
+    tail_split = get("EDM_TAIL_SPLIT", kTailMaxParts);
   }
 };
 const Tuning& tuning() {
@@ -47,6 +50,10 @@ void apply_tuning(LaunchParams& lp) {
   lp.stage_limit = tuning().stage_limit;
   lp.band = tuning().band;
   lp.push_stride = tuning().push_stride;
+  lp.tail_split = tuning().tail_split;
+  // flags of the split last wave carry a value no earlier launch of this process used
+  static std::atomic<uint32_t> tail_epoch{0};
+  lp.tail_epoch = tail_epoch.fetch_add(1u) + 1u;
 }
 
 #define EDM_CUDA(expr)                                   \
@@ -630,6 +637,8 @@ int edm_status_clear(void) {
   uint32_t z[16] = {};
   EDM_CUDA(cudaDeviceSynchronize());
   EDM_CUDA(cudaMemcpyToSymbol(g_status, z, sizeof(z)));
+  // a launch that gave up may have left the claim counters of the split last wave part-way
+  EDM_CUDA(cudaMemcpyToSymbol(g_tail_next, z, sizeof(uint32_t) * kMaxVirtualRanks));
   return EDM_OK;
 }
 int edm_profile_enable(int on) {
@@ -775,6 +784,13 @@ int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m,
     out[4 * i + 2] = t.owner;
     out[4 * i + 3] = t.owned_idx;
   }
+  return EDM_OK;
+}
+
+int edm_tail_split(int64_t tiles, int units, int64_t k_blocks, int32_t out[3]) {
+  if (tiles < 0 || tiles > INT32_MAX || units < 1 || k_blocks < 1 || k_blocks > INT32_MAX || !out) return EDM_ERR_BAD_ARG;
+  const TailSplit t(static_cast<int>(tiles), units, static_cast<int>(k_blocks), tuning().tail_split);
+  out[0] = t.first; out[1] = t.tiles; out[2] = t.parts;
   return EDM_OK;
 }
 

@@ -33,6 +33,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <climits>
 #include <cstdint>
 #include "ptx.cuh"
 
@@ -64,6 +65,7 @@ enum Status : uint32_t {
   kTimeoutPartialFlag = 5,   // RS/AR: a peer's partial tile never arrived
   kTimeoutResultFlag = 6,    // AR: an owner's reduced tile never arrived
   kTimeoutGatherFlag = 7,    // AG: a peer's shard chunk never arrived
+  kTimeoutTailFlag = 8,      // split last wave: another CTA's partial sum never arrived
 };
 
 __device__ uint32_t g_status[16];
@@ -123,6 +125,8 @@ struct LaunchParams {
   int32_t stage_limit;    // experiments: use at most this many ring stages (0 = all)
   int32_t push_stride;    // all-gather: only CTAs whose index is a multiple of this push the shard
   int32_t band;           // row blocks per band of the tile walk (0 = default)
+  int32_t tail_split;     // most pieces a tile of an incomplete last wave is cut into along K (< 2: none)
+  uint32_t tail_epoch;    // value the partial-sum flags of this launch carry
   RankParams r[kMaxVirtualRanks];
 };
 
@@ -305,6 +309,62 @@ struct TileWalk {
   }
 };
 
+// ------------------------------------------------------------------ split of the last wave
+// `units` CTAs (or pairs) take tiles round-robin, so when the tile count is not a multiple of
+// `units` the last wave leaves most of them idle for a whole tile time (160 tiles on 74 pairs: the
+// third wave has 12).  Those `tiles` tail tiles are instead cut along K into `parts` pieces that
+// run side by side.  Pieces are not assigned in advance: a unit that has finished its whole tiles
+// claims the next piece from a counter, piece index = tile * parts + piece, so the pieces of one
+// tile go to units that became free at about the same time (units drift apart by tens of
+// microseconds over a launch) and the slowest units get none.  The pieces of a tile exchange fp32
+// partial sums through scratch tiles and each finishes its share of the tile's columns (see
+// tail_piece in the kernel).
+constexpr int kTailMinKBlocks = 16;   // a piece is at least this many K blocks (2 us of MMA work)
+constexpr int kTailMaxParts = 8;
+constexpr int kTailMaxCtas = 160;     // CTAs the static scratch below has room for
+struct TailSplit {
+  int first;   // tiles (walk positions) below this are computed whole, round-robin
+  int tiles;   // tail tiles
+  int parts;   // pieces per tail tile (1: nothing is split)
+  // max_parts: most pieces per tile (a power of two up to kTailMaxParts; < 2 switches the split off)
+  __host__ __device__ TailSplit(int positions, int units, int k_blocks, int max_parts) {
+    first = positions; tiles = 0; parts = 1;
+    const int full = units > 0 ? positions / units * units : 0;
+    const int rest = positions - full;
+    if (max_parts >= 2 && full > 0 && rest > 0) {
+      int s = units / rest;
+      if (s > k_blocks / kTailMinKBlocks) s = k_blocks / kTailMinKBlocks;
+      if (s > kTailMaxParts) s = kTailMaxParts;
+      if (s > max_parts) s = max_parts;
+      while (s & (s - 1)) s &= s - 1;  // a power of two: each piece finishes whole 32-column chunks
+      if (s >= 2) { first = full; tiles = rest; parts = s; }
+    }
+  }
+  __host__ __device__ int pieces() const { return parts > 1 ? tiles * parts : 0; }
+  // claimed piece -> position in the tile walk, piece of the tile and its K-block range
+  __host__ __device__ void piece(int idx, int k_blocks, int& pos, int& part, int& k_lo, int& k_hi) const {
+    const int r = idx / parts;
+    part = idx - r * parts;
+    pos = first + r;
+    k_lo = static_cast<int>(static_cast<int64_t>(k_blocks) * part / parts);
+    k_hi = static_cast<int>(static_cast<int64_t>(k_blocks) * (part + 1) / parts);
+  }
+};
+// One work item of a CTA: a whole tile (n_parts == 1) or a piece of a tail tile.
+struct Work {
+  int pos;            // position in the tile walk
+  int part, n_parts;  // piece of the tile
+  int k_lo, k_hi;     // K blocks
+  int piece;          // claimed piece index (slot of its scratch tile and flags)
+};
+// Scratch tiles and flags of the pieces (one fp32 tile and one flag per epilogue warp per piece
+// and CTA of a pair), the claim counter per (virtual) rank, and the word through which the warp
+// that claimed tells the other warps of its CTA pair: launch epoch << 32 | piece index.
+__device__ float g_tail_scratch[static_cast<size_t>(kTailMaxCtas) * kBlockM * kBlockN];
+__device__ uint32_t g_tail_flags[kTailMaxCtas * 4];
+__device__ uint32_t g_tail_next[kMaxVirtualRanks];
+__device__ unsigned long long g_tail_claim[kTailMaxCtas];
+
 // ------------------------------------------------------------------ descriptors
 // K-major operand tile in shared memory, 128B rows, 128B swizzle, 8-row groups 1024B apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -483,6 +543,57 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const int seg_kb = (P.seg_kblocks > 0 && P.seg_kblocks < num_kb_pass) ? P.seg_kblocks : num_kb_pass;
   const int num_segs = (num_kb_pass + seg_kb - 1) / seg_kb;
   const int rows_per_rank = P.world > 0 ? P.M / P.world : P.M;
+  // only launches that write their tiles in place split the last wave (fused reductions end on
+  // local tiles anyway; the split-fp32 path already uses its accumulator segments)
+  const TailSplit tail(walk.positions, num_ctas, num_kb_pass,
+                       (kBN == 256 && (P.mode == kPlain || P.mode == kAG) && P.passes == 1 && num_segs == 1 &&
+                        gridDim.x <= kTailMaxCtas) ? lp.tail_split : 0);
+
+  // Work items of this CTA, in order: its whole tiles, then at most one claimed piece of a tail
+  // tile.  `claim` is called once, when the whole tiles are done: the producer thread of the
+  // unit's first CTA takes the next piece index from the counter and publishes it; every other
+  // role waits for that word.
+  const int first_cta_of_unit = static_cast<int>(blockIdx.x) - static_cast<int>(pr);
+  auto claim_piece = [&]() -> int {
+    const uint32_t got = atomicAdd(&g_tail_next[vr], 1u);
+    // every unit claims exactly once per launch: the last one leaves the counter at zero
+    if (got == static_cast<uint32_t>(num_ctas) - 1u) atomicExch(&g_tail_next[vr], 0u);
+    *reinterpret_cast<volatile unsigned long long*>(&g_tail_claim[first_cta_of_unit]) =
+        (static_cast<unsigned long long>(lp.tail_epoch) << 32) | got;
+    return static_cast<int>(got);
+  };
+  auto await_piece = [&]() -> int {
+    const volatile unsigned long long* word = &g_tail_claim[first_cta_of_unit];
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+      const unsigned long long v = *word;
+      if (static_cast<uint32_t>(v >> 32) == lp.tail_epoch) return static_cast<int>(v & 0xFFFFFFFFull);
+      if ((spins++ & 31u) == 0u) {
+        if (aborted()) return INT_MAX;
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > timeout_ns) { report(kTimeoutTailFlag, 0xFFFFu, lp.tail_epoch, static_cast<uint32_t>(v >> 32)); return INT_MAX; }
+      }
+      __nanosleep(64);
+    }
+  };
+  // advances (i, tail_taken); false when this CTA has nothing left
+  auto next_work = [&](int& i, bool& tail_taken, bool claims, Work& w) -> bool {
+    if (i < tail.first) {
+      w.pos = i; w.part = 0; w.n_parts = 1; w.k_lo = 0; w.k_hi = num_kb_pass; w.piece = -1;
+      i += num_ctas;
+      return true;
+    }
+    if (tail.parts == 1 || tail_taken) return false;
+    tail_taken = true;
+    const int idx = claims ? claim_piece() : await_piece();
+    if (idx >= tail.pieces()) return false;
+    tail.piece(idx, num_kb_pass, w.pos, w.part, w.k_lo, w.k_hi);
+    w.n_parts = tail.parts;
+    w.piece = idx;
+    return true;
+  };
 
   // ------------------------------------------------------------------ all-gather pushes
   // Five warps per CTA (2, 3, 9, 10, 11) copy the local shard into every peer's gather buffer with
@@ -667,8 +778,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       uint32_t it = 0, s = 0, ph = 0;  // ring position: stage and the phase bit of its current use
       uint64_t seen_chunks = 0;        // all-gather chunks whose flag this CTA has already acquired
       const int prof_empty = prof ? kProfProducerEmptyWait : -1;
-      for (int i = cta; i < walk.positions; i += num_ctas) {
-        const Tile t = walk.at(i);
+      Work w;
+      bool tail_taken = false;
+      for (int i = cta; next_work(i, tail_taken, pr == 0, w);) {
+        const int k_lo = w.k_lo, k_hi = w.k_hi;
+        const Tile t = walk.at(w.pos);
         if (!t.valid) continue;
         const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM;  // this CTA's rows of A
         const int n0 = t.n_blk * kBN + static_cast<int>(pr) * (kBN / kCG);  // its rows of B
@@ -709,7 +823,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           }
         }
         for (int seg = 0; seg < num_segs; ++seg) {
-          const int j0 = seg * seg_kb, j1 = min(j0 + seg_kb, num_kb_pass);
+          const int j0 = k_lo + seg * seg_kb, j1 = min(j0 + seg_kb, k_hi);
           for (int pass = 0; pass < P.passes; ++pass) {
             // split fp32: (lo,hi), (hi,lo), then (hi,hi) so the small terms meet a small accumulator
             const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
@@ -741,14 +855,17 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       uint32_t s = 0, ph = 0;     // ring position: stage and the phase bit of its current use
       const uint64_t adesc0 = make_smem_desc(smem_base);
       const int prof_full = prof ? kProfMmaFullWait : -1, prof_tmem = prof ? kProfMmaTmemWait : -1;
-      for (int i = cta; i < walk.positions; i += num_ctas) {
-        if (!walk.at(i).valid) continue;
+      Work w;
+      bool tail_taken = false;
+      for (int i = cta; next_work(i, tail_taken, false, w);) {
+        const int k_lo = w.k_lo, k_hi = w.k_hi;
+        if (!walk.at(w.pos).valid) continue;
         for (int seg = 0; seg < num_segs; ++seg, ++unit) {
           const uint32_t acc = unit & 1u;
           wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit, prof_tmem);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kBN;
-          const int nkb = (min((seg + 1) * seg_kb, num_kb_pass) - seg * seg_kb) * P.passes;
+          const int nkb = (min(k_lo + (seg + 1) * seg_kb, k_hi) - (k_lo + seg * seg_kb)) * P.passes;
           for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
             wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it, prof_full);
             tc_fence_after();
@@ -798,43 +915,144 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // running fp32 sums of this thread's row: [chunk][row][32 floats], private to the CTA
     float* my_scratch = P.scratch == nullptr ? nullptr
         : P.scratch + (static_cast<size_t>(blockIdx.x) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
-    for (int i = cta; i < walk.positions; i += num_ctas) {
-      const Tile t = walk.at(i);
+    // partial sums of a piece of a split tail tile: this thread's row in this CTA's scratch tile
+    // scratch tile / flags of piece `idx` for this CTA's half of the tile
+    auto tail_slot = [&](int idx) { return vr * lp.ctas_per_vrank + idx * kCG + static_cast<int>(pr); };
+    // accumulator `u` -> fp32 tile at dst ([32-column chunk][row][32 floats]), optionally added to what is there
+    auto dump_accumulator = [&](uint32_t u, float* dst, bool add) {
+      const uint32_t sacc = u & 1u;
+      if (lane == 0)
+        wait_mbar(bar_tfull + 8 * sacc, (u >> 1) & 1u, timeout_ns, kTimeoutTmemFull, u);
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t staddr = tmem_base + sacc * kBN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(staddr + c * 32, raw);
+        tmem_ld_wait();
+        float4* sp = reinterpret_cast<float4*>(dst + static_cast<size_t>(c) * kBlockM * 32);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          float4 x = make_float4(__uint_as_float(raw[4 * w]), __uint_as_float(raw[4 * w + 1]),
+                                 __uint_as_float(raw[4 * w + 2]), __uint_as_float(raw[4 * w + 3]));
+          if (add) {
+            const float4 y = sp[w];
+            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+          }
+          sp[w] = x;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * sacc);
+        else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * sacc, 0));
+      }
+    };
+    // One of the `n_parts` pieces (K ranges) of a split tail tile.  The pieces run at the same time
+    // on different CTAs and finish the tile together: piece p owns the 32-column chunks
+    // [p, p+1) * 8 / n_parts of the tile.  It leaves its partial sums of all other chunks in its
+    // scratch tile, raises its flag, waits for the other pieces' flags, adds their partial sums of
+    // its own chunks to its accumulator and writes those columns of the output.
+    auto tail_piece = [&](const Tile& t, const Work& wk, uint32_t u) {
+      const int part = wk.part, n_parts = wk.n_parts;
+      const int my_slot = tail_slot(wk.piece), slot0 = tail_slot(wk.piece - part);  // own, and piece 0 of the tile
+      float* const tail_mine = g_tail_scratch + (static_cast<size_t>(my_slot) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
+      const uint32_t acc = u & 1u;
+      // (accounting slots of the reducer and of the fused epilogue double for the pieces' exchange)
+      ProfTimer piece_total(eprof);
+      if (lane == 0) {
+        ProfTimer pt(eprof);
+        wait_mbar(bar_tfull + 8 * acc, (u >> 1) & 1u, timeout_ns, kTimeoutTmemFull, u);
+        pt.stop(kProfEpiTmemWait);
+      }
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
+      ProfTimer pdump(eprof);
+      const int per = (kBN / 32) / n_parts, c_lo = part * per, c_hi = c_lo + per;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        if (c >= c_lo && c < c_hi) continue;
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        uint4* sp = reinterpret_cast<uint4*>(tail_mine + static_cast<size_t>(c) * kBlockM * 32);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sp[w] = make_uint4(raw[4 * w], raw[4 * w + 1], raw[4 * w + 2], raw[4 * w + 3]);
+      }
+      pdump.stop(kProfEpiIssue);
+      ProfTimer pfence(eprof);
+      __threadfence();
+      __syncwarp();
+      pfence.stop(kProfEpiFence);
+      if (lane == 0) st_relaxed_sys(&g_tail_flags[my_slot * 4 + q], lp.tail_epoch);
+      ProfTimer pwait(eprof);
+      if (lane < n_parts && lane != part)
+        wait_flag(&g_tail_flags[(slot0 + lane * kCG) * 4 + q], lp.tail_epoch, timeout_ns,
+                  kTimeoutTailFlag, lane);
+      __syncwarp();
+      pwait.stop(kProfReducerFlagWait);
+      const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBN;
+      char* out_row = static_cast<char*>(P.out) + (static_cast<int64_t>(m0 + row) * P.ld_out + n0) * kOutBytes;
+#pragma unroll 1
+      for (int c = c_lo; c < c_hi; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+#pragma unroll 1
+        for (int p = 0; p < n_parts; ++p) {
+          if (p == part) continue;
+          const char* sp = reinterpret_cast<const char*>(
+              g_tail_scratch + (static_cast<size_t>(slot0 + p * kCG) * kBlockM * kBlockN +
+                                static_cast<size_t>(c) * kBlockM * 32 + static_cast<size_t>(row) * 32));
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const uint4 y = ld_cg_v4(sp + w * 16);
+            v[4 * w] += __uint_as_float(y.x); v[4 * w + 1] += __uint_as_float(y.y);
+            v[4 * w + 2] += __uint_as_float(y.z); v[4 * w + 3] += __uint_as_float(y.w);
+          }
+        }
+        if (m0 + row < P.M) {
+#pragma unroll
+          for (int w = 0; w < 32 / kOutPerVec; ++w) {
+            uint4 o;
+            if constexpr (kOutBytes == 2) {
+              o = OutPack<__nv_bfloat16>::pack8(&v[w * 8]);
+            } else {
+              o.x = __float_as_uint(v[w * 4 + 0]); o.y = __float_as_uint(v[w * 4 + 1]);
+              o.z = __float_as_uint(v[w * 4 + 2]); o.w = __float_as_uint(v[w * 4 + 3]);
+            }
+            const int col = c * 32 + w * kOutPerVec;
+            if (n0 + col < P.N) st_global_v4(out_row + col * kOutBytes, o);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * acc);
+        else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+      }
+      piece_total.stop(kProfReducerTotal);
+    };
+    Work w;
+    bool tail_taken = false;
+    for (int i = cta; next_work(i, tail_taken, false, w);) {
+      const Tile t = walk.at(w.pos);
       if (!t.valid) continue;
+      if (w.n_parts > 1) {
+        tail_piece(t, w, unit++);
+        continue;
+      }
       // this CTA's 128-row half of the tile: its slot / flag index at the owner
       const int slot_idx = t.owned_idx * kCG + static_cast<int>(pr);
       // every segment but the last is only folded into the running sum
-      for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) {
-        const uint32_t sacc = unit & 1u;
-        if (lane == 0)
-          wait_mbar(bar_tfull + 8 * sacc, (unit >> 1) & 1u, timeout_ns, kTimeoutTmemFull, unit);
-        __syncwarp();
-        tc_fence_after();
-        const uint32_t staddr = tmem_base + sacc * kBN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t raw[32];
-          tmem_ld_32x32(staddr + c * 32, raw);
-          tmem_ld_wait();
-          float4* sp = reinterpret_cast<float4*>(my_scratch + static_cast<size_t>(c) * kBlockM * 32);
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            float4 x = make_float4(__uint_as_float(raw[4 * w]), __uint_as_float(raw[4 * w + 1]),
-                                   __uint_as_float(raw[4 * w + 2]), __uint_as_float(raw[4 * w + 3]));
-            if (seg > 0) {
-              const float4 y = sp[w];
-              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-            }
-            sp[w] = x;
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * sacc);
-          else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * sacc, 0));
-        }
-      }
+      for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) dump_accumulator(unit, my_scratch, seg > 0);
       const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
       if (lane == 0) {
@@ -853,7 +1071,6 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       }
       __syncwarp();
       tc_fence_after();
-
       // Where the tile goes.  Fused modes: every tile -- this rank's own included -- is shipped
       // as a partial into the owner's window slot [source rank][slot]; the owner's reducer warps
       // add the slots up.  Otherwise it is written to the output in place.

@@ -206,3 +206,11 @@ def tile_walk(op: str, rank: int, world: int, M: int, N: int, tile_m: int = 256,
     _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, units, buf, n.value,
                                  C.byref(n)), "edm_tile_walk")
     return [tuple(buf[4 * i:4 * i + 4]) for i in range(n.value)]
+
+
+def tail_split(tiles: int, units: int, k_blocks: int) -> tuple[int, int, int]:
+    """``(whole_tiles, split_tiles, pieces)``: how a launch of ``tiles`` tiles on ``units`` CTAs (or
+    pairs) cuts the tiles of an incomplete last wave along K (``pieces == 1``: not at all)."""
+    out = (C.c_int32 * 3)()
+    _lib.check(_lib.load().edm_tail_split(tiles, units, k_blocks, out), "edm_tail_split")
+    return int(out[0]), int(out[1]), int(out[2])

@@ -144,6 +144,15 @@ int edm_comm_p2p_probe(edm_comm_t* comm, int peer, size_t bytes, int mode, void*
  * ranks agree on owners and slots. */
 int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m, int tile_n, int band_rows,
                   int units, int32_t* out, int64_t capacity, int64_t* positions);
+/* How a launch of `tiles` output tiles on `units` CTAs (or CTA pairs) with `k_blocks` blocks of 128
+ * bytes along K treats an incomplete last wave (host-side evaluation, no device work):
+ * out[0] = tiles computed whole, out[1] = tiles of the last wave that are split along K,
+ * out[2] = pieces per split tile (1 = nothing is split).  Piece p of a split tile covers K blocks
+ * [k_blocks * p / pieces, k_blocks * (p + 1) / pieces); CTAs claim pieces from a device counter as
+ * they finish their whole tiles.
+ * Applies to EDM_OP_GEMM and EDM_OP_AG_GEMM in bf16 with 256-wide tiles.  No reference
+ * counterpart; used by the CPU tests. */
+int edm_tail_split(int64_t tiles, int units, int64_t k_blocks, int32_t out[3]);
 int edm_comm_rank(const edm_comm_t* comm);
 int edm_comm_world(const edm_comm_t* comm);
 

@@ -28,6 +28,8 @@ def _rand(shape, scale, dtype, seed):
     (1000, 768, 520), (130, 264, 72), (8, 8, 8),           # ragged M, N, K edges
     (5, 1000, 264), (128, 40, 4096),                       # narrow (128x32) tiles with a ragged last tile
     (1024, 4096, 3584),
+    (2560, 2048, 8192), (2500, 2000, 4104),                # 80 tiles on 74 CTA pairs: last wave cut in 8 / 4 along K
+    (200, 20480, 2048),                                    # 160 tiles on 148 CTAs: last wave cut in 2
 ])
 def test_gemm_bf16_matches_oracle(cuda_clean, M, N, K):
     a = _rand((M, K), 1.0, torch.bfloat16, 1)
@@ -68,9 +70,10 @@ def test_strided_operands_and_output(cuda_clean):
     assert torch.count_nonzero(out_full[:, N:]) == 0  # nothing written past N
 
 
-def test_selection_matrix_is_bit_exact_at_full_size(cuda_clean):
-    # rows of A are one-hot, so D[m, n] must equal B[n, k(m)] exactly; full down_proj extents
-    M, N, K = 8192, 8192, 3584
+@pytest.mark.parametrize("M,N,K", [(8192, 8192, 3584), (8192, 1280, 8192)])
+def test_selection_matrix_is_bit_exact_at_full_size(cuda_clean, M, N, K):
+    # rows of A are one-hot, so D[m, n] must equal B[n, k(m)] exactly; full down_proj extents, and
+    # the qkv extents whose last wave of tiles is cut along K (partial sums of 0 and one value)
     g = torch.Generator(device="cpu").manual_seed(7)
     pick = torch.randint(0, K, (M,), generator=g)
     a = torch.zeros(M, K, dtype=torch.bfloat16)

@@ -90,6 +90,30 @@ def test_all_gather_walk_follows_arrival_order(native_lib, world):
             assert first[s] > last[s - 2]
 
 
+def test_split_of_the_last_wave(native_lib):
+    # the layer's shapes on 74 CTA pairs (K blocks of 64 bf16)
+    assert symm.tail_split(32 * 5, 74, 128) == (148, 12, 4)      # qkv: 160 tiles, third wave of 12
+    assert symm.tail_split(32 * 28, 74, 128) == (888, 8, 8)      # gate_up: 896 tiles, last wave of 8
+    assert symm.tail_split(32 * 32, 74, 56) == (1024, 0, 1)      # down: last wave of 62, left alone
+    assert symm.tail_split(32 * 32, 74, 16) == (1024, 0, 1)      # o_proj: K too short to cut
+    assert symm.tail_split(20, 74, 128) == (20, 0, 1)            # less than one wave: left alone
+    for tiles in range(1, 400, 7):
+        for units in (1, 2, 37, 74, 148):
+            for kb in (1, 15, 16, 40, 128, 448):
+                first, split, parts = symm.tail_split(tiles, units, kb)
+                assert first + split == tiles
+                assert parts in (1, 2, 4, 8)
+                if parts > 1:
+                    assert first % units == 0 and first >= units      # whole waves before the tail
+                    assert split * parts <= units                     # one piece per unit at most
+                    assert kb // parts >= 16                          # every piece has work to do
+                    # the pieces' K ranges tile [0, kb) without gaps
+                    edges = [kb * p // parts for p in range(parts + 1)]
+                    assert edges[0] == 0 and edges[-1] == kb and all(a < b for a, b in zip(edges, edges[1:]))
+                else:
+                    assert split == 0
+
+
 def test_bad_arguments(native_lib):
     with pytest.raises(ValueError):
         symm.tile_walk("gemm_rs", 2, 2, 1024, 1024)
