@@ -14,7 +14,8 @@ Prints ONE JSON line on rank 0.  ``value`` is microseconds per layer, device-tim
 events on the launching stream, maximum over ranks.  ``e2e`` is the same layer driven through
 the public operators from pinned host buffers: host->device copies of the step's activations
 and device->host copies of its outputs are inside the timed region (weights are parameters
-and stay resident).
+and stay resident); ``edmir_b200.host_io.HostStaging`` keeps uploads, kernels and downloads on
+three streams, and a step ends when all its results are in host memory.
 
 ``--impl reference`` times the CPU restatement of the path (the oracle; the reference itself
 has no implementation of it) on the host cores instead.
@@ -183,7 +184,7 @@ def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
 
-    from edmir_b200 import linear, symm
+    from edmir_b200 import host_io, linear, symm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -305,11 +306,13 @@ def run_ours(args) -> None:
         extra["cublas_matmul_us"] = round(timed(unfused_layer, sub_steps, 3), 2)
 
     # end to end from pinned host buffers
+    staging = host_io.HostStaging(dev)
     def e2e_step():
+        # uploads, kernels and downloads on three streams; the step ends (on the timed stream)
+        # when every result of the step is in host memory
         for o in ops:
-            o["a"].copy_(o["a_host"], non_blocking=True)
-            launch(o)
-            o["out_host"].copy_(o["out"], non_blocking=True)
+            staging.run(o["a_host"], o["a"], lambda o=o: launch(o), o["out"], o["out_host"])
+        staging.drain()
     e2e_steps = max(3, min(args.steps, 20))
     e2e_us = None if args.quick else timed(e2e_step, e2e_steps, 3)
     h2d = sum(o["a_host"].numel() * 2 for o in ops)
