@@ -219,12 +219,21 @@ int launch_variant(int dtype, int cg, int bn, const LaunchParams& lp, int grid, 
 }
 
 // Tile width of the plain bf16 GEMM.  With a single row block (M <= 128: decode) the job is to
-// stream the weights once, so 128x32 tiles spread N over all SMs; otherwise 256 wide.
-int pick_block_n(int dtype, int cg, int64_t M, int64_t N, int sms) {
+// stream the weights once through as many SMs as possible.  Two ways to get there: 128x32 tiles
+// (8x more tiles, each CTA re-reads its 128 rows of A over the whole K), or 128x256 tiles cut along
+// K over the idle CTAs (TailSplit; the pieces then exchange partial sums).  Measured per CTA:
+// 0.30 us per K block with narrow tiles, 0.54 us per K block plus 7.4 us for the exchange with
+// wide pieces; the choice compares the two.
+int pick_block_n(int dtype, int cg, int64_t M, int64_t N, int64_t K, int sms) {
   if (dtype != EDM_DTYPE_BF16 || cg != 1) return kBlockN;
   if (tuning().block_n == 32 || tuning().block_n == 256) return tuning().block_n;
   const int64_t wide_tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
-  return (M <= kBlockM && wide_tiles * 2 <= sms) ? 32 : kBlockN;
+  if (M > kBlockM || wide_tiles * 2 > sms) return kBlockN;
+  const int64_t kb = (K * 2 + kBlockKBytes - 1) / kBlockKBytes;
+  const TailSplit split(static_cast<int>(wide_tiles), sms, static_cast<int>(kb), tuning().tail_split);
+  const int64_t narrow_ns = 300 * kb;
+  const int64_t wide_ns = 540 * ((kb + split.parts - 1) / split.parts) + (split.parts > 1 ? 7400 : 0);
+  return wide_ns < narrow_ns ? kBlockN : 32;
 }
 
 int max_resident_ctas(int dtype, int cg, int sms, int* out) {
@@ -301,6 +310,57 @@ int check_dims(int64_t M, int64_t N, int64_t K) {
   return EDM_OK;
 }
 
+// CTAs of a launch over `tiles` tiles: one unit (CTA or pair) per tile up to what fits on the GPU,
+// or, with fewer tiles than units and a launch that may cut tiles along K, one unit per piece.
+int grid_for_tiles(int tiles, int cg, int resident, bool may_split, int64_t K, int max_parts) {
+  const int units = resident / cg;
+  if (tiles >= units) return units * cg;
+  int work = tiles;
+  if (may_split) {
+    const TailSplit split(tiles, units, static_cast<int>((K * 2 + kBlockKBytes - 1) / kBlockKBytes), max_parts);
+    if (split.parts > 1) work = split.tiles * split.parts;
+  }
+  return (work < units ? work : units) * cg;
+}
+
+// Launches that may cut tiles along K share one scratch array, claim counter and flag set per
+// device.  Two of them on the same stream are ordered anyway; across streams this event keeps them
+// apart (a launch waits for the previous one that was issued on another stream).  Launches under
+// stream capture are left alone: whoever builds the graph orders them.
+struct ScratchGuard {
+  std::mutex mu;
+  cudaEvent_t ev = nullptr;
+  cudaStream_t last = nullptr;
+  bool recorded = false;
+};
+ScratchGuard* scratch_guard() {
+  static ScratchGuard guards[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return &guards[dev];
+}
+bool capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  return cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
+}
+int scratch_guard_before(cudaStream_t s) {
+  ScratchGuard* g = scratch_guard();
+  if (!g || capturing(s)) return EDM_OK;
+  std::lock_guard<std::mutex> lock(g->mu);
+  if (g->recorded && g->last != s) EDM_CUDA(cudaStreamWaitEvent(s, g->ev, 0));
+  return EDM_OK;
+}
+int scratch_guard_after(cudaStream_t s) {
+  ScratchGuard* g = scratch_guard();
+  if (!g || capturing(s)) return EDM_OK;
+  std::lock_guard<std::mutex> lock(g->mu);
+  if (!g->ev) EDM_CUDA(cudaEventCreateWithFlags(&g->ev, cudaEventDisableTiming));
+  EDM_CUDA(cudaEventRecord(g->ev, s));
+  g->last = s;
+  g->recorded = true;
+  return EDM_OK;
+}
+
 int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
                int64_t M, int64_t N, int64_t K, void* ws, size_t ws_bytes, void* stream) {
   if (!a || !b || !d) return EDM_ERR_BAD_ARG;
@@ -316,7 +376,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   const int cg = pick_cta_group(dtype, EDM_OP_GEMM, M, 1);
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
-  const int bn = pick_block_n(dtype, cg, M, N, sms);
+  const int bn = pick_block_n(dtype, cg, M, N, K, sms);
   rc = prepare_operands(P, dtype, cg, bn, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
   if (rc) return rc;
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
@@ -325,13 +385,15 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   int resident = 0;
   if ((rc = max_resident_ctas(dtype, cg, sms, &resident))) return rc;
   const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + bn - 1) / bn));
-  const int grid = tiles * cg < resident ? tiles * cg : resident;
+  apply_tuning(lp);
+  const int grid = grid_for_tiles(tiles, cg, resident, bn == kBlockN && dtype == EDM_DTYPE_BF16, K, lp.tail_split);
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  apply_tuning(lp);
-  return launch_variant(dtype, cg, bn, lp, grid, false, s);
+  if ((rc = scratch_guard_before(s))) return rc;
+  if ((rc = launch_variant(dtype, cg, bn, lp, grid, false, s))) return rc;
+  return scratch_guard_after(s);
 }
 
 }  // namespace
@@ -833,8 +895,11 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   apply_tuning(lp);
   const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
   if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
+  const bool may_split = lp.r[0].mode == kAG;  // the only fused mode that writes its tiles in place
+  if (may_split && (rc = scratch_guard_before(s))) return rc;
   rc = launch_variant(call->dtype, cg, kBlockN, lp, grid, false, s);
   if (rc) return rc;
+  if (may_split && (rc = scratch_guard_after(s))) return rc;
   if (ce) return ag_copy_engine_after_launch(comm, s);
   return EDM_OK;
 }
@@ -866,8 +931,10 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   apply_tuning(lp);
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
+  if ((rc = scratch_guard_before(s))) return rc;
   rc = launch_variant(calls[0].dtype, cg, kBlockN, lp, lp.ctas_per_vrank * n, true, s);
   if (rc) return rc;
+  if ((rc = scratch_guard_after(s))) return rc;
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_after_launch(comms[i], s))) return rc;
   return EDM_OK;

@@ -104,6 +104,13 @@ __device__ __forceinline__ void bulk_store(void* dst_global, uint32_t src_smem, 
                "r"(src_smem), "r"(bytes)
                : "memory");
 }
+// Bulk copy global -> this CTA's shared memory; completes `bytes` on the mbarrier.  Addresses and
+// size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src_global, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src_global), "r"(bytes), "r"(mbar)
+               : "memory");
+}
 // Wait until at most N of this thread's most recent bulk groups are still pending (fully written).
 template <int N>
 __device__ __forceinline__ void bulk_wait_pending() {

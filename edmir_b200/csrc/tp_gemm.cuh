@@ -312,14 +312,15 @@ struct TileWalk {
 // ------------------------------------------------------------------ split of the last wave
 // `units` CTAs (or pairs) take tiles round-robin, so when the tile count is not a multiple of
 // `units` the last wave leaves most of them idle for a whole tile time (160 tiles on 74 pairs: the
-// third wave has 12).  Those `tiles` tail tiles are instead cut along K into `parts` pieces that
-// run side by side.  Pieces are not assigned in advance: a unit that has finished its whole tiles
+// third wave has 12; a decode-sized GEMM has fewer tiles than units to begin with).  Those `tiles`
+// tail tiles are instead cut along K into `parts` pieces that run side by side.  Pieces are not assigned in advance: a unit that has finished its whole tiles
 // claims the next piece from a counter, piece index = tile * parts + piece, so the pieces of one
 // tile go to units that became free at about the same time (units drift apart by tens of
 // microseconds over a launch) and the slowest units get none.  The pieces of a tile exchange fp32
 // partial sums through scratch tiles and each finishes its share of the tile's columns (see
 // tail_piece in the kernel).
-constexpr int kTailMinKBlocks = 16;   // a piece is at least this many K blocks (2 us of MMA work)
+constexpr int kTailMinKBlocks = 4;    // a piece is at least this many K blocks
+constexpr int kTailMinTileKBlocks = 32;  // shorter tiles are not cut: the exchange (~7 us) would cost more than it saves
 constexpr int kTailMaxParts = 8;
 constexpr int kTailMaxCtas = 160;     // CTAs the static scratch below has room for
 struct TailSplit {
@@ -331,7 +332,9 @@ struct TailSplit {
     first = positions; tiles = 0; parts = 1;
     const int full = units > 0 ? positions / units * units : 0;
     const int rest = positions - full;
-    if (max_parts >= 2 && full > 0 && rest > 0) {
+    // (full == 0: fewer tiles than units, e.g. a decode-sized GEMM; every tile is a tail tile then
+    // and the launch is a split-K GEMM over otherwise idle CTAs)
+    if (max_parts >= 2 && rest > 0 && k_blocks >= kTailMinTileKBlocks) {
       int s = units / rest;
       if (s > k_blocks / kTailMinKBlocks) s = k_blocks / kTailMinKBlocks;
       if (s > kTailMaxParts) s = kTailMaxParts;
@@ -458,9 +461,8 @@ template <> struct OutPack<float> {
 // cta_group::2 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its own
 // 128 accumulator rows, so the epilogue is the same per-CTA code in both variants.
 // kBN = tile width: 256, or 32 for decode-sized M (one row block): 128x32 tiles give every SM a
-// slab of the weights to stream instead of leaving most SMs idle (plain GEMM only).  Such a launch
-// is bound by the issue cost of its K/16 MMA instructions per CTA, not by memory; splitting K
-// over CTAs would be the next step for those shapes.
+// slab of the weights to stream instead of leaving most SMs idle (plain GEMM only; for long K the
+// host prefers 256-wide tiles cut along K over the idle CTAs, see TailSplit).
 template <int kCG, int kBN, bool kTf32, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
@@ -479,7 +481,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   constexpr int kOutPerVec = 16 / kOutBytes;               // 8 / 4
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[2 * kMaxStages + 4];
+  __shared__ uint64_t bars[2 * kMaxStages + 8];
   __shared__ uint32_t tmem_base_slot;
   __shared__ Mailbox mbox[kMailboxes];
   __shared__ uint32_t reduce_next;  // next (half-tile, quarter) unit of the reduction
@@ -504,6 +506,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_empty = smem_u32(&bars[kStages]);
   const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
+  const uint32_t bar_tail = smem_u32(&bars[2 * kMaxStages + 4]);  // one per epilogue warp: partial sums have landed
   // all-gather mode gives the last ring stage to the push warps as staging buffers
   const bool ag_push = P.mode == kAG && P.world > 1 && !P.ag_external;
   uint32_t stages = kStages;
@@ -522,6 +525,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
     }
+    for (int w = 0; w < 4; ++w) mbar_init(bar_tail + 8 * w, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -958,7 +962,12 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     auto tail_piece = [&](const Tile& t, const Work& wk, uint32_t u) {
       const int part = wk.part, n_parts = wk.n_parts;
       const int my_slot = tail_slot(wk.piece), slot0 = tail_slot(wk.piece - part);  // own, and piece 0 of the tile
-      float* const tail_mine = g_tail_scratch + (static_cast<size_t>(my_slot) * kBlockM * kBlockN + static_cast<size_t>(row) * 32);
+      // A scratch tile is 32 blocks of 4 KiB, block (chunk c, warp q) = the warp's 32 rows x 32
+      // columns as [8 vectors][32 rows] x 16 bytes: a warp writes and reads 512 contiguous bytes
+      // per instruction, and a block moves with one bulk copy.
+      constexpr uint32_t kBlk = 4096;
+      constexpr size_t kTileBytes = static_cast<size_t>(kBlockM) * kBlockN * 4;
+      char* const scratch = reinterpret_cast<char*>(g_tail_scratch);
       const uint32_t acc = u & 1u;
       // (accounting slots of the reducer and of the fused epilogue double for the pieces' exchange)
       ProfTimer piece_total(eprof);
@@ -978,9 +987,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         uint32_t raw[32];
         tmem_ld_32x32(taddr + c * 32, raw);
         tmem_ld_wait();
-        uint4* sp = reinterpret_cast<uint4*>(tail_mine + static_cast<size_t>(c) * kBlockM * 32);
+        char* blk = scratch + my_slot * kTileBytes + static_cast<size_t>(c * 4 + q) * kBlk + lane * 16;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) sp[w] = make_uint4(raw[4 * w], raw[4 * w + 1], raw[4 * w + 2], raw[4 * w + 3]);
+        for (int w = 0; w < 8; ++w)
+          st_global_v4(blk + w * 512, make_uint4(raw[4 * w], raw[4 * w + 1], raw[4 * w + 2], raw[4 * w + 3]));
       }
       pdump.stop(kProfEpiIssue);
       ProfTimer pfence(eprof);
@@ -993,6 +1003,22 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         wait_flag(&g_tail_flags[(slot0 + lane * kCG) * 4 + q], lp.tail_epoch, timeout_ns,
                   kTimeoutTailFlag, lane);
       __syncwarp();
+      // The other pieces' partial sums of this piece's chunks come in with bulk copies, all in
+      // flight at once, into operand-ring space (the ring is idle: this piece was the CTA's last
+      // work and its MMAs have completed).  At most 7 blocks per warp.
+      const uint32_t land = smem_base + static_cast<uint32_t>(q) * 7u * kBlk;
+      const uint32_t my_bar = bar_tail + 8 * q;
+      if (lane == 0) {
+        fence_proxy_async_global();  // written with ordinary stores by the peers, read by a bulk copy here
+        mbar_arrive_expect_tx(my_bar, static_cast<uint32_t>((n_parts - 1) * per) * kBlk);
+        uint32_t dst = land;
+        for (int p = 0; p < n_parts; ++p) {
+          if (p == part) continue;
+          for (int c = c_lo; c < c_hi; ++c, dst += kBlk)
+            bulk_load(dst, scratch + (slot0 + p * kCG) * kTileBytes + static_cast<size_t>(c * 4 + q) * kBlk, kBlk, my_bar);
+        }
+      }
+      wait_mbar(my_bar, 0u, timeout_ns, kTimeoutTailFlag, 0x100u | static_cast<uint32_t>(q));
       pwait.stop(kProfReducerFlagWait);
       const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBN;
       char* out_row = static_cast<char*>(P.out) + (static_cast<int64_t>(m0 + row) * P.ld_out + n0) * kOutBytes;
@@ -1005,14 +1031,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
 #pragma unroll 1
-        for (int p = 0; p < n_parts; ++p) {
-          if (p == part) continue;
-          const char* sp = reinterpret_cast<const char*>(
-              g_tail_scratch + (static_cast<size_t>(slot0 + p * kCG) * kBlockM * kBlockN +
-                                static_cast<size_t>(c) * kBlockM * 32 + static_cast<size_t>(row) * 32));
+        for (int k = 0; k < n_parts - 1; ++k) {
+          const uint32_t blk = land + static_cast<uint32_t>(k * per + (c - c_lo)) * kBlk + lane * 16;
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
-            const uint4 y = ld_cg_v4(sp + w * 16);
+            const uint4 y = ld_shared_v4(blk + w * 512);
             v[4 * w] += __uint_as_float(y.x); v[4 * w + 1] += __uint_as_float(y.y);
             v[4 * w + 2] += __uint_as_float(y.z); v[4 * w + 3] += __uint_as_float(y.w);
           }

@@ -30,6 +30,8 @@ def _rand(shape, scale, dtype, seed):
     (1024, 4096, 3584),
     (2560, 2048, 8192), (2500, 2000, 4104),                # 80 tiles on 74 CTA pairs: last wave cut in 8 / 4 along K
     (200, 20480, 2048),                                    # 160 tiles on 148 CTAs: last wave cut in 2
+    (128, 4096, 7168), (16, 4096, 14336), (1, 4096, 7168),  # decode: 16 wide tiles cut in 8 along K
+    (100, 520, 4104), (64, 8192, 3584),                    # ragged pieces; 32 tiles cut in 4
 ])
 def test_gemm_bf16_matches_oracle(cuda_clean, M, N, K):
     a = _rand((M, K), 1.0, torch.bfloat16, 1)

@@ -96,17 +96,19 @@ def test_split_of_the_last_wave(native_lib):
     assert symm.tail_split(32 * 28, 74, 128) == (888, 8, 8)      # gate_up: 896 tiles, last wave of 8
     assert symm.tail_split(32 * 32, 74, 56) == (1024, 0, 1)      # down: last wave of 62, left alone
     assert symm.tail_split(32 * 32, 74, 16) == (1024, 0, 1)      # o_proj: K too short to cut
-    assert symm.tail_split(20, 74, 128) == (20, 0, 1)            # less than one wave: left alone
+    assert symm.tail_split(20, 74, 128) == (0, 20, 2)            # less than one wave: every tile is cut
+    assert symm.tail_split(16, 148, 112) == (0, 16, 8)           # decode-sized GEMM: split-K over idle CTAs
+    assert symm.tail_split(16, 148, 28) == (16, 0, 1)            # K too short for the exchange to pay
     for tiles in range(1, 400, 7):
         for units in (1, 2, 37, 74, 148):
-            for kb in (1, 15, 16, 40, 128, 448):
+            for kb in (1, 8, 16, 31, 32, 40, 128, 448):
                 first, split, parts = symm.tail_split(tiles, units, kb)
                 assert first + split == tiles
                 assert parts in (1, 2, 4, 8)
                 if parts > 1:
-                    assert first % units == 0 and first >= units      # whole waves before the tail
+                    assert first % units == 0                         # whole waves before the tail
                     assert split * parts <= units                     # one piece per unit at most
-                    assert kb // parts >= 16                          # every piece has work to do
+                    assert kb >= 32 and kb // parts >= 4              # every piece has work to do
                     # the pieces' K ranges tile [0, kb) without gaps
                     edges = [kb * p // parts for p in range(parts + 1)]
                     assert edges[0] == 0 and edges[-1] == kb and all(a < b for a, b in zip(edges, edges[1:]))
