@@ -47,7 +47,7 @@ JSON_OUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch (gate_up, 55 % of the layer's
 # flops), from the ncu capture summarised in profiles/tp_gemm_bf16_layer_1gpu.md
-NCU_TRAFFIC_BYTES_GATE_UP = 1_091_324_000 + 110_513_664
+NCU_TRAFFIC_BYTES_GATE_UP = 1_080_005_000 + 111_048_960
 
 
 def load_peaks():
