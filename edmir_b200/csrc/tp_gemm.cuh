@@ -25,6 +25,9 @@
 // (it drains the SM), so no working warp ever executes one: they post "this data has landed"
 // notes into shared-memory mailboxes and the signaller turns batches of notes into one fence plus
 // relaxed flag stores.
+// Tiles are dealt round-robin to the CTAs (pairs); the tiles of an incomplete last wave -- or all
+// tiles, when there are fewer than CTAs -- are cut along K into pieces that free CTAs claim from a
+// counter and whose partial sums they exchange through scratch tiles (TailSplit, tail_piece).
 // Accumulators are double buffered in TMEM (2 x 256 columns) so the epilogue of tile i, which
 // is where the NVLink traffic is issued, overlaps the MMAs of tile i+1.
 //
@@ -507,7 +510,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
   const uint32_t bar_tail = smem_u32(&bars[2 * kMaxStages + 4]);  // one per epilogue warp: partial sums have landed
-  // all-gather mode gives the last ring stage to the push warps as staging buffers
+  // all-gather with the sm transport: warps 2, 3 and 9-11 push this rank's shard to the peers
   const bool ag_push = P.mode == kAG && P.world > 1 && !P.ag_external;
   uint32_t stages = kStages;
   if (lp.stage_limit > 0 && static_cast<uint32_t>(lp.stage_limit) < stages) stages = lp.stage_limit;
