@@ -86,6 +86,30 @@ def test_selection_matrix_is_bit_exact_at_full_size(cuda_clean, M, N, K):
     assert torch.equal(out, want)
 
 
+def test_split_k_launches_replay_from_a_cuda_graph(cuda_clean):
+    # pieces are claimed from a device counter that the last claimer resets: replays of a captured
+    # launch must find it at zero every time and give the eager result bit for bit
+    a = _rand((64, 7168), 1.0, torch.bfloat16, 21).cuda()
+    b = _rand((4096, 7168), 0.02, torch.bfloat16, 22).cuda()
+    want = linear.gemm(a, b).clone()
+    out = torch.zeros_like(want)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        linear.gemm(a, b, out)          # first use of the variant outside capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):
+                linear.gemm(a, b, out)
+        for _ in range(3):
+            out.zero_()
+            graph.replay()
+            side.synchronize()
+            assert torch.equal(out, want)
+    torch.cuda.current_stream().wait_stream(side)
+    assert torch.equal(linear.gemm(a, b), want)   # and eager launches still work afterwards
+
+
 def test_repeatable_bit_for_bit(cuda_clean):
     a = _rand((2048, 1024), 1.0, torch.bfloat16, 9).cuda()
     b = _rand((2048, 1024), 0.02, torch.bfloat16, 10).cuda()
