@@ -25,6 +25,7 @@ class Calibration:
     ``gemm_tflops``: sustained bf16 rate of the GEMM kernel at large shapes.
     ``gemm_tile_us``: time of one wave of tiles at K=1024 (sets the floor for small shapes).
     ``link_gbs``: bytes per nanosecond a GPU pushes into peers' windows, per direction.
+    ``ag_link_gbs``: what the copy engines (the default all-gather transport) deliver per direction.
     ``publish_ns``: latency from "data landed" to "flag visible" (one system-scope fence batch).
     ``launch_ns``: cost of one more kernel / collective launch on the stream.
     ``nccl_gbs``: what the unfused collective sustains per direction (for the c = 1 candidate).
@@ -33,6 +34,7 @@ class Calibration:
     name: str = "B200"
     gemm_tflops: float = 1400.0
     link_gbs: float = 660.0
+    ag_link_gbs: float = 470.0
     nccl_gbs: float = 380.0
     publish_ns: int = 15_000
     launch_ns: int = 8_000
@@ -43,7 +45,7 @@ class Calibration:
     def load(cls, path: str = DEFAULT_TABLE) -> "Calibration":
         with open(path) as f:
             raw = json.load(f)
-        known = {k: raw[k] for k in ("name", "gemm_tflops", "link_gbs", "nccl_gbs", "publish_ns",
+        known = {k: raw[k] for k in ("name", "gemm_tflops", "link_gbs", "ag_link_gbs", "nccl_gbs", "publish_ns",
                                      "launch_ns", "split_ns") if k in raw}
         return cls(**known, extra={k: v for k, v in raw.items() if k not in known})
 
@@ -72,10 +74,11 @@ def cost_params(op: str, M: int, N: int, K: int, world: int, calib: Calibration,
 
     ``fused=False`` describes the unfused sequence (library GEMM, then an NCCL collective): the
     collective runs at ``nccl_gbs`` and pays a launch; ``fused=True`` describes in-kernel pushes at
-    ``link_gbs`` where a chunk costs one flag publication."""
+    ``link_gbs`` (copy-engine deliveries at ``ag_link_gbs`` for the all-gather) where a chunk costs
+    one flag publication."""
     flops = 2 * M * N * K
     gemm_ns = int(round(flops / (calib.gemm_tflops * 1e3)))  # TFLOP/s = 1e3 flop/ns
-    gbs = calib.link_gbs if fused else calib.nccl_gbs
+    gbs = calib.nccl_gbs if not fused else (calib.ag_link_gbs if op == "ag_gemm" else calib.link_gbs)
     # transfer ns = bytes / (GB/s) ; keep it rational: bytes * 1000 / (gbs * 1000) with integer gbs
     beta_den = max(int(round(gbs)), 1)
     return CostParams(
