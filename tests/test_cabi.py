@@ -4,6 +4,8 @@ import ctypes as C
 import os
 import re
 
+import pytest
+
 from edmir_b200 import _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -51,3 +53,12 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib._build, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_host_staging_needs_a_device():
+    import torch
+    from edmir_b200 import host_io
+    if torch.cuda.is_available():
+        pytest.skip("covered by the GPU suite")
+    with pytest.raises(RuntimeError):
+        host_io.HostStaging()
