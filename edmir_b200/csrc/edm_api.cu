@@ -46,11 +46,19 @@ const Tuning& tuning() {
   static const Tuning t;
   return t;
 }
-void apply_tuning(LaunchParams& lp) {
+bool capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  return cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
+}
+// Most pieces a tile may be cut into along K by a launch on `s`.  The pieces' flags carry a launch
+// counter kept on the host; a replay of a captured launch would repeat its value and find the
+// flags of the previous replay already raised, so captured launches do not split.
+int max_tail_parts(cudaStream_t s) { return capturing(s) ? 0 : tuning().tail_split; }
+void apply_tuning(LaunchParams& lp, cudaStream_t s) {
   lp.stage_limit = tuning().stage_limit;
   lp.band = tuning().band;
   lp.push_stride = tuning().push_stride;
-  lp.tail_split = tuning().tail_split;
+  lp.tail_split = max_tail_parts(s);
   // flags of the split last wave carry a value no earlier launch of this process used
   static std::atomic<uint32_t> tail_epoch{0};
   lp.tail_epoch = tail_epoch.fetch_add(1u) + 1u;
@@ -224,13 +232,13 @@ int launch_variant(int dtype, int cg, int bn, const LaunchParams& lp, int grid, 
 // K over the idle CTAs (TailSplit; the pieces then exchange partial sums).  Measured per CTA:
 // 0.30 us per K block with narrow tiles, 0.54 us per K block plus 7.4 us for the exchange with
 // wide pieces; the choice compares the two.
-int pick_block_n(int dtype, int cg, int64_t M, int64_t N, int64_t K, int sms) {
+int pick_block_n(int dtype, int cg, int64_t M, int64_t N, int64_t K, int sms, int max_parts) {
   if (dtype != EDM_DTYPE_BF16 || cg != 1) return kBlockN;
   if (tuning().block_n == 32 || tuning().block_n == 256) return tuning().block_n;
   const int64_t wide_tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
   if (M > kBlockM || wide_tiles * 2 > sms) return kBlockN;
   const int64_t kb = (K * 2 + kBlockKBytes - 1) / kBlockKBytes;
-  const TailSplit split(static_cast<int>(wide_tiles), sms, static_cast<int>(kb), tuning().tail_split);
+  const TailSplit split(static_cast<int>(wide_tiles), sms, static_cast<int>(kb), max_parts);
   const int64_t narrow_ns = 300 * kb;
   const int64_t wide_ns = 540 * ((kb + split.parts - 1) / split.parts) + (split.parts > 1 ? 7400 : 0);
   return wide_ns < narrow_ns ? kBlockN : 32;
@@ -339,10 +347,6 @@ ScratchGuard* scratch_guard() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   return &guards[dev];
 }
-bool capturing(cudaStream_t s) {
-  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-  return cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
-}
 int scratch_guard_before(cudaStream_t s) {
   ScratchGuard* g = scratch_guard();
   if (!g || capturing(s)) return EDM_OK;
@@ -376,7 +380,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   const int cg = pick_cta_group(dtype, EDM_OP_GEMM, M, 1);
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
-  const int bn = pick_block_n(dtype, cg, M, N, K, sms);
+  const int bn = pick_block_n(dtype, cg, M, N, K, sms, max_tail_parts(s));
   rc = prepare_operands(P, dtype, cg, bn, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
   if (rc) return rc;
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
@@ -385,7 +389,7 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   int resident = 0;
   if ((rc = max_resident_ctas(dtype, cg, sms, &resident))) return rc;
   const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + bn - 1) / bn));
-  apply_tuning(lp);
+  apply_tuning(lp, s);
   const int grid = grid_for_tiles(tiles, cg, resident, bn == kBlockN && dtype == EDM_DTYPE_BF16, K, lp.tail_split);
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
@@ -892,7 +896,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  apply_tuning(lp);
+  apply_tuning(lp, s);
   const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
   if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
   const bool may_split = lp.r[0].mode == kAG;  // the only fused mode that writes its tiles in place
@@ -928,7 +932,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   if (lp.ctas_per_vrank < cg) return EDM_ERR_CUDA;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  apply_tuning(lp);
+  apply_tuning(lp, s);
   for (int i = 0; i < n; ++i)
     if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
   if ((rc = scratch_guard_before(s))) return rc;
