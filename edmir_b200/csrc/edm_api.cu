@@ -884,6 +884,9 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the exchange flags carry the context's call counter, which a replay of a captured launch
+  // would repeat: fused launches cannot be captured
+  if (comm->world > 1 && capturing(s)) return EDM_ERR_UNSUPPORTED;
   const int cg = pick_cta_group(call->dtype, call->op, call->M, comm->world);
   int rc = build_rank_params(comm, *call, cg, lp.r[0], s);
   if (rc) return rc;
@@ -913,6 +916,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (capturing(s)) return EDM_ERR_UNSUPPORTED;  // see edm_tp_launch
   const int cg = pick_cta_group(calls[0].dtype, calls[0].op, calls[0].M, comms[0] ? comms[0]->world : 1);
   for (int i = 0; i < n; ++i) {
     if (!comms[i] || calls[i].dtype != calls[0].dtype || calls[i].op != calls[0].op ||

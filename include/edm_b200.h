@@ -82,7 +82,9 @@ int edm_set_timeout_ms(uint32_t ms);
 
 /* ---- single-GPU GEMM ---------------------------------------------------------------
  * Replaces run_tiled_mma / tiled_mma_bf16_bf16_bf16_fp32 (EDM-IR/ir/c-extension/mma.cu:168-271)
- * for arbitrary M, N, K.  Asynchronous on `stream`. */
+ * for arbitrary M, N, K.  Asynchronous on `stream`.  May be issued under stream capture (captured
+ * launches use a schedule without cross-CTA K-splitting, whose flags depend on a host-side launch
+ * counter). */
 int edm_gemm_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
                   int64_t M, int64_t N, int64_t K, void* stream);
 
@@ -176,6 +178,8 @@ typedef struct {
   size_t workspace_bytes;
 } edm_tp_call_t;
 
+/* Not capturable: the flags of the exchange carry the context's call counter, which a graph replay
+ * would repeat; with world > 1 a launch on a capturing stream returns EDM_ERR_UNSUPPORTED. */
 int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream);
 
 /* Runs n ranks' calls as ONE cooperative launch on the current device (rank i uses 1/n of the
