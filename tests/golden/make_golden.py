@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py <reference checkout>/EDM-IR
 
-Imports the reference's own ``ir`` package (default ``/root/reference/EDM-IR``) and writes:
+Imports the reference's own ``ir`` package from the directory given on the command line and writes:
 * ``analysis_golden.json`` -- the graphs of the reference's tests (tests/analysis_test.py:16-58)
   and demo (examples/synthetic_demo.py:24-128) serialised node by node, with the reference's
   ``analyze_critical_path`` / ``analyze_exposure`` / ``phase_duration_us`` outputs;
@@ -21,7 +21,9 @@ import os
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/EDM-IR"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <reference checkout>/EDM-IR")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 import ir  # noqa: E402  (the reference package)
