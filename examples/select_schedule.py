@@ -13,7 +13,7 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from edmir_b200 import lowering  # noqa: E402
+from edmir_b200 import graph_json, lowering  # noqa: E402
 from edmir_b200.calibration import Calibration  # noqa: E402
 from edmir_b200.ir.printing import format_summary, format_uops  # noqa: E402
 
@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=8)
     ap.add_argument("--candidates", default="1,2,4,8")
     ap.add_argument("--show-graphs", action="store_true")
+    ap.add_argument("--save-graph", metavar="PATH", help="write the chosen candidate's EDM graph as JSON")
     args = ap.parse_args()
 
     spec = lowering.TPLinearSpec(args.op, args.tokens, args.n, args.k, args.tp)
@@ -41,6 +42,8 @@ def main() -> None:
         g = sel.graphs[sel.chosen]
         print(format_uops(g, highlight=g.critical_path()[0]))
         print(format_summary(g))
+    if args.save_graph:
+        graph_json.save(sel.graphs[sel.chosen], args.save_graph)
 
 
 if __name__ == "__main__":
