@@ -100,6 +100,7 @@ SIGNATURES = {
     "edm_comm_p2p_probe": (C.c_int, [_vp, C.c_int, _sz, C.c_int, _vp]),
     "edm_tile_walk": (C.c_int, [C.c_int, C.c_int, C.c_int, _i64, _i64, C.c_int, C.c_int, C.c_int, C.c_int,
                                 C.POINTER(C.c_int32), _i64, C.POINTER(_i64)]),
+    "edm_gemm_plan": (C.c_int, [_i64, _i64, _i64, C.c_int, C.POINTER(C.c_int32)]),
     "edm_tail_split": (C.c_int, [_i64, C.c_int, _i64, C.POINTER(C.c_int32)]),
     "edm_comm_rank": (C.c_int, [_vp]),
     "edm_comm_world": (C.c_int, [_vp]),

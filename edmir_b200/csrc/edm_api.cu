@@ -853,6 +853,22 @@ int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m,
   return EDM_OK;
 }
 
+int edm_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int32_t out[4]) {
+  if (!out || sms < 2 || sms > 4096) return EDM_ERR_BAD_ARG;
+  int rc = check_dims(M, N, K);
+  if (rc) return rc;
+  const int max_parts = tuning().tail_split;
+  const int cg = pick_cta_group(EDM_DTYPE_BF16, EDM_OP_GEMM, M, 1);
+  const int bn = pick_block_n(EDM_DTYPE_BF16, cg, M, N, K, sms, max_parts);
+  const int resident = cg == 2 ? sms - sms % 2 : sms;
+  const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + bn - 1) / bn));
+  const int grid = grid_for_tiles(tiles, cg, resident, bn == kBlockN, K, max_parts);
+  const TailSplit split(tiles, grid / cg, static_cast<int>((K * 2 + kBlockKBytes - 1) / kBlockKBytes),
+                        bn == kBlockN ? max_parts : 0);
+  out[0] = cg; out[1] = bn; out[2] = grid; out[3] = split.parts;
+  return EDM_OK;
+}
+
 int edm_tail_split(int64_t tiles, int units, int64_t k_blocks, int32_t out[3]) {
   if (tiles < 0 || tiles > INT32_MAX || units < 1 || k_blocks < 1 || k_blocks > INT32_MAX || !out) return EDM_ERR_BAD_ARG;
   const TailSplit t(static_cast<int>(tiles), units, static_cast<int>(k_blocks), tuning().tail_split);

@@ -127,6 +127,14 @@ def tiled_mma_bf16_bf16_bf16_fp32(a: torch.Tensor, b: torch.Tensor,
     return (acc + c).to(torch.bfloat16)
 
 
+def gemm_plan(M: int, N: int, K: int, sms: int = 148) -> dict:
+    """What ``gemm`` would launch for this shape on a GPU with ``sms`` SMs: CTAs per tile, tile
+    width, CTAs launched and the number of pieces split tiles are cut into along K (host only)."""
+    out = (C.c_int32 * 4)()
+    _lib.check(_lib.load().edm_gemm_plan(M, N, K, sms, out), "edm_gemm_plan")
+    return {"cta_group": int(out[0]), "block_n": int(out[1]), "ctas": int(out[2]), "pieces": int(out[3])}
+
+
 def status() -> list[int]:
     """Device status words (all zero unless a bounded device-side wait expired)."""
     buf = (C.c_uint32 * 16)()

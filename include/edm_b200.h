@@ -155,6 +155,12 @@ int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m,
  * Applies to EDM_OP_GEMM and EDM_OP_AG_GEMM in bf16 with 256-wide tiles.  No reference
  * counterpart; used by the CPU tests. */
 int edm_tail_split(int64_t tiles, int units, int64_t k_blocks, int32_t out[3]);
+/* What edm_gemm_bf16 would launch for an [M, N, K] problem on a GPU with `sms` SMs (host-side
+ * evaluation of the launch heuristics, no device work): out[0] = CTAs per tile (1, or 2 for CTA
+ * pairs on 256-row tiles), out[1] = tile width (256 or 32), out[2] = CTAs launched, out[3] = pieces
+ * a tile of an incomplete last wave (or every tile, when there are fewer tiles than CTAs) is cut
+ * into along K (1 = none).  No reference counterpart; used by the CPU tests. */
+int edm_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int32_t out[4]);
 int edm_comm_rank(const edm_comm_t* comm);
 int edm_comm_world(const edm_comm_t* comm);
 

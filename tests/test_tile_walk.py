@@ -121,3 +121,22 @@ def test_bad_arguments(native_lib):
         symm.tile_walk("gemm_rs", 2, 2, 1024, 1024)
     with pytest.raises(ValueError):
         symm.tile_walk("gemm_rs", 0, 2, 1024 + 128, 1024)   # rows per rank not on tile edges
+
+
+def test_launch_plans_of_the_layer_and_of_decode_shapes(native_lib):
+    from edmir_b200 import linear
+    plan = lambda *shape: tuple(linear.gemm_plan(*shape).values())   # (cta_group, block_n, ctas, pieces)
+    # prefill layer at 8192 tokens: CTA pairs on every SM; qkv and gate_up cut their last wave
+    assert plan(8192, 1280, 8192) == (2, 256, 148, 4)
+    assert plan(8192, 7168, 8192) == (2, 256, 148, 8)
+    assert plan(8192, 8192, 1024) == (2, 256, 148, 1)
+    assert plan(8192, 8192, 3584) == (2, 256, 148, 1)
+    # decode rows of the 8B down_proj: split-K over 128 CTAs for long K, narrow tiles for short K
+    assert plan(16, 4096, 14336) == (1, 256, 128, 8)
+    assert plan(128, 4096, 7168) == (1, 256, 128, 8)
+    assert plan(128, 4096, 1792) == (1, 32, 128, 1)
+    assert plan(1, 4096, 1792) == (1, 32, 128, 1)
+    # 64 pair tiles on 74 pairs: nothing to cut
+    assert plan(1024, 4096, 3584) == (2, 256, 128, 1)
+    with pytest.raises(ValueError):
+        linear.gemm_plan(0, 16, 16)
