@@ -102,7 +102,7 @@ def test_config1_all_reduce_fp32(cuda_clean, group_factory):
 @pytest.mark.parametrize("transport", ["sm", "ce"])
 @pytest.mark.parametrize("world,M,N,K,chunks", [(2, 512, 512, 256, 2), (4, 2048, 768, 512, 4), (4, 256, 768, 512, 1),
                                                 (2, 1024, 264, 1000, 3), (4, 4096, 512, 1024, 8),
-                                                (2, 2048, 1280, 2048, 2),   # 40 tiles on 37 pairs: tail cut in 2
+                                                (2, 2048, 1280, 2048, 2),   # 40 tiles on 37 pairs: tail cut in 8
                                                 (2, 1024, 512, 4096, 2)])   # 8 tiles on 37 pairs: every tile cut in 4
 def test_all_gather_gemm(cuda_clean, group_factory, world, M, N, K, chunks, transport):
     g = group_factory(world)

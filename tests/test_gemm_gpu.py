@@ -28,8 +28,8 @@ def _rand(shape, scale, dtype, seed):
     (1000, 768, 520), (130, 264, 72), (8, 8, 8),           # ragged M, N, K edges
     (5, 1000, 264), (128, 40, 4096),                       # narrow (128x32) tiles with a ragged last tile
     (1024, 4096, 3584),
-    (2560, 2048, 8192), (2500, 2000, 4104),                # 80 tiles on 74 CTA pairs: last wave cut in 8 / 4 along K
-    (200, 20480, 2048),                                    # 160 tiles on 148 CTAs: last wave cut in 2
+    (2560, 2048, 8192), (2500, 2000, 4104),                # 80 tiles on 74 CTA pairs: last wave cut in 8 along K
+    (200, 20480, 2048),                                    # 160 tiles on 148 CTAs: last wave cut in 8
     (128, 4096, 7168), (16, 4096, 14336), (1, 4096, 7168),  # decode: 16 wide tiles cut in 8 along K
     (100, 520, 4104), (64, 8192, 3584),                    # ragged pieces; 32 tiles cut in 4
 ])
