@@ -28,6 +28,7 @@ EDM_OP_AG_GEMM = 3
 
 EDM_TRANSPORT_SM = 0
 EDM_TRANSPORT_COPY_ENGINE = 1
+EDM_TRANSPORT_HYBRID = 2
 
 EDM_MAX_RANKS = 8
 EDM_IPC_HANDLE_BYTES = 64
@@ -53,6 +54,8 @@ class TpCall(C.Structure):
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
         ("chunks", C.c_int32), ("transport", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("pusher_ctas", C.c_int32), ("ce_peers", C.c_int32), ("side_streams", C.c_int32),
+        ("band_rows", C.c_int32), ("band_cols", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -83,6 +86,7 @@ SIGNATURES = {
     "edm_last_cuda_error": (C.c_int, []),
     "edm_status_read": (C.c_int, [C.POINTER(C.c_uint32)]),
     "edm_status_clear": (C.c_int, []),
+    "edm_status_check": (C.c_int, []),
     "edm_set_timeout_ms": (C.c_int, [C.c_uint32]),
     "edm_profile_enable": (C.c_int, [C.c_int]),
     "edm_profile_read": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
@@ -97,8 +101,9 @@ SIGNATURES = {
     "edm_comm_link_local": (C.c_int, [_vp, C.c_int, _vp]),
     "edm_comm_heap_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp)]),
     "edm_comm_heap_reset": (C.c_int, [_vp]),
+    "edm_comm_poison": (C.c_int, [_vp, C.c_int, _vp]),
     "edm_comm_p2p_probe": (C.c_int, [_vp, C.c_int, _sz, C.c_int, _vp]),
-    "edm_tile_walk": (C.c_int, [C.c_int, C.c_int, C.c_int, _i64, _i64, C.c_int, C.c_int, C.c_int, C.c_int,
+    "edm_tile_walk": (C.c_int, [C.c_int, C.c_int, C.c_int, _i64, _i64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                 C.POINTER(C.c_int32), _i64, C.POINTER(_i64)]),
     "edm_gemm_plan": (C.c_int, [_i64, _i64, _i64, C.c_int, C.POINTER(C.c_int32)]),
     "edm_tail_split": (C.c_int, [_i64, C.c_int, _i64, C.POINTER(C.c_int32)]),
@@ -110,6 +115,9 @@ SIGNATURES = {
     "edm_gemm_ar_bf16": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_ag_gemm_bf16": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "edm_schedule_cost": (C.c_int, [C.POINTER(CostParams), _i32, C.POINTER(CandidateCost)]),
+    "edm_graph_cost": (C.c_int, [_i32, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(C.c_uint8), _i32,
+                                 C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i64), C.POINTER(_i64),
+                                 C.POINTER(_i32), C.POINTER(_i32)]),
     "edm_select_schedule": (C.c_int, [C.POINTER(CostParams), C.POINTER(_i32), _i32,
                                       C.POINTER(CandidateCost), C.POINTER(_i32)]),
 }

@@ -34,15 +34,25 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+CHECKED_LIB_PATH = os.path.join(PKG_DIR, "libedm_b200_checked.so")
+
+
+def build_checked(verbose: bool = False) -> str:
+    """Compile the checking variant (``-DEDM_DEBUG_BOUNDS``): every global address the kernel
+    computes is validated against the ranges the launch may touch and violations are reported
+    through the status words instead of faulting.  Select it with ``EDM_LIB_PATH``."""
+    return build(force=True, verbose=verbose, out=CHECKED_LIB_PATH, defines=("EDM_DEBUG_BOUNDS",))
+
+
+def build(force: bool = False, verbose: bool = False, out: str = LIB_PATH, defines: tuple = ()) -> str:
     """Compile the library if it is missing or older than its sources; return its path."""
-    if not force and not _stale():
+    if out == LIB_PATH and not force and not _stale():
         return LIB_PATH
     cmd = [
         _nvcc(), "-shared", "-Xcompiler", "-fPIC", "-std=c++17", "-O3", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
-        "-o", LIB_PATH,
-    ] + [os.path.join(CSRC, s) for s in SOURCES]
+        "-o", out,
+    ] + [f"-D{d}" for d in defines] + [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -50,9 +60,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode != 0:
-        raise RuntimeError("nvcc failed building libedm_b200.so")
-    return LIB_PATH
+        raise RuntimeError(f"nvcc failed building {os.path.basename(out)}")
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--checked" in sys.argv:
+        print(build_checked(verbose="--verbose" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -3,14 +3,15 @@
 The reference's model leaves its parameters to measurement ("calibrated from nccl-tests, P2P
 tests, and serving traces", paper/mlsys-2027/model.md:111) and ships none.  This module holds
 the ones measured on B200 with this library's own kernels (``edm_comm_p2p_probe`` for the link,
-the GEMM kernel for the compute rate) and turns a layer shape into the integer
-``CostParams`` (nanoseconds) the selector consumes.
+the GEMM kernel for the compute rate, the fused launches for the fixed costs) and turns a layer
+shape into the integer ``CostParams`` (nanoseconds) the chunk-count selector consumes.
+``lowering.schedule_graph`` uses the same table for the per-schedule candidate graphs.
 """
 from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, fields
 
 from .selector import CostParams
 
@@ -20,39 +21,59 @@ DEFAULT_TABLE = os.path.join(_HERE, "calibration_b200.json")
 
 @dataclass(frozen=True)
 class Calibration:
-    """Measured figures of one device class.
+    """Measured figures of one device class (rates in GB/s = bytes per nanosecond).
 
-    ``gemm_tflops``: sustained bf16 rate of the GEMM kernel at large shapes.
-    ``gemm_tile_us``: time of one wave of tiles at K=1024 (sets the floor for small shapes).
-    ``link_gbs``: bytes per nanosecond a GPU pushes into peers' windows, per direction.
-    ``ag_link_gbs``: what the copy engines (the default all-gather transport) deliver per direction.
+    ``gemm_tflops``: bf16 rate of the GEMM kernel on all ``gemm_units`` CTA pairs at large shapes.
+    ``tile_ns_per_kblock`` / ``tile_fixed_ns``: time a CTA pair spends per 64-element K block of a
+      256x256 tile and per tile (fill, drain, epilogue hand-over); they set the cost of short-K tiles.
+    ``link_gbs``: what one GPU pushes into its peers' windows per direction with every SM storing.
+    ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
+    ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams.
+    ``sm_push_slowdown``: factor on the GEMM when warps inside every GEMM CTA push the shard.
     ``publish_ns``: latency from "data landed" to "flag visible" (one system-scope fence batch).
-    ``launch_ns``: cost of one more kernel / collective launch on the stream.
-    ``nccl_gbs``: what the unfused collective sustains per direction (for the c = 1 candidate).
+    ``launch_ns``: start-up and tear-down of one fused launch; ``ce_launch_ns``: what the stream
+      operations of the copy-engine transport add per launch.
+    ``skew_ns_per_rank``: what waiting for the slowest of W ranks adds to a launch that needs data
+      from every peer, per additional rank.
+    ``reduce_gbs``: rate at which an owner adds up partial tiles (reads of all W slots).
+    ``nccl_gbs``: what the unfused library collective sustains per direction (comparison baseline).
     """
 
     name: str = "B200"
-    gemm_tflops: float = 1400.0
-    link_gbs: float = 660.0
+    gemm_tflops: float = 1450.0
+    gemm_units: int = 74
+    tile_ns_per_kblock: int = 100
+    tile_fixed_ns: int = 1_200
+    link_gbs: float = 650.0
+    pusher_cta_gbs: float = 45.0
+    ce_gbs: tuple = (290.0, 470.0, 470.0, 470.0)
     ag_link_gbs: float = 470.0
+    sm_push_slowdown: float = 1.17
     nccl_gbs: float = 380.0
+    reduce_gbs: float = 2500.0
     publish_ns: int = 15_000
-    launch_ns: int = 8_000
+    launch_ns: int = 12_000
+    ce_launch_ns: int = 35_000
+    skew_ns_per_rank: int = 4_000
     split_ns: int = 2_000
-    extra: dict = field(default_factory=dict)
+    extra: dict = field(default_factory=dict, compare=False, hash=False)
 
     @classmethod
     def load(cls, path: str = DEFAULT_TABLE) -> "Calibration":
         with open(path) as f:
             raw = json.load(f)
-        known = {k: raw[k] for k in ("name", "gemm_tflops", "link_gbs", "ag_link_gbs", "nccl_gbs", "publish_ns",
-                                     "launch_ns", "split_ns") if k in raw}
-        return cls(**known, extra={k: v for k, v in raw.items() if k not in known})
+        names = {f.name for f in fields(cls)} - {"extra"}
+        known = {k: (tuple(v) if isinstance(v, list) else v) for k, v in raw.items() if k in names}
+        return cls(**known, extra={k: v for k, v in raw.items() if k not in names})
 
     def as_device_table(self) -> dict:
         """Fields for ``ir.device.install_calibration``."""
         return {"nvlink_gbs_per_dir": self.link_gbs, "bf16_tflops": self.gemm_tflops,
                 "flag_publish_ns": self.publish_ns, **self.extra}
+
+    def ce_rate(self, side_streams: int) -> float:
+        n = min(max(side_streams, 1), len(self.ce_gbs))
+        return float(self.ce_gbs[n - 1])
 
 
 def wire_bytes(op: str, M: int, N: int, K: int, world: int, elem_bytes: int = 2) -> int:
@@ -68,25 +89,37 @@ def wire_bytes(op: str, M: int, N: int, K: int, world: int, elem_bytes: int = 2)
     raise ValueError(f"unknown op {op}")
 
 
+def gemm_ns(M: int, N: int, K: int, calib: Calibration, units: int | None = None, elem_bytes: int = 2) -> int:
+    """Time of the GEMM alone on ``units`` CTA pairs: whole waves of 256x256 tiles, each costing
+    its K blocks plus a fixed part, but never less than the flops at the calibrated rate."""
+    units = calib.gemm_units if units is None else max(units, 1)
+    tiles = -(-M // 256) * -(-N // 256)
+    k_blocks = -(-K * elem_bytes // 128)
+    waves = -(-tiles // units)
+    by_tiles = waves * (k_blocks * calib.tile_ns_per_kblock + calib.tile_fixed_ns)
+    by_rate = int(round(2 * M * N * K / (calib.gemm_tflops * 1e3) * calib.gemm_units / units))  # TFLOP/s = 1e3 flop/ns
+    return max(by_tiles, by_rate)
+
+
 def cost_params(op: str, M: int, N: int, K: int, world: int, calib: Calibration,
                 fused: bool = True) -> CostParams:
-    """Integer (nanosecond) model inputs for one layer call.
+    """Integer (nanosecond) inputs of the chunk-count model for one layer call.
 
     ``fused=False`` describes the unfused sequence (library GEMM, then an NCCL collective): the
     collective runs at ``nccl_gbs`` and pays a launch; ``fused=True`` describes in-kernel pushes at
     ``link_gbs`` (copy-engine deliveries at ``ag_link_gbs`` for the all-gather) where a chunk costs
     one flag publication."""
     flops = 2 * M * N * K
-    gemm_ns = int(round(flops / (calib.gemm_tflops * 1e3)))  # TFLOP/s = 1e3 flop/ns
+    total = int(round(flops / (calib.gemm_tflops * 1e3)))
     gbs = calib.nccl_gbs if not fused else (calib.ag_link_gbs if op == "ag_gemm" else calib.link_gbs)
-    # transfer ns = bytes / (GB/s) ; keep it rational: bytes * 1000 / (gbs * 1000) with integer gbs
+    # transfer ns = bytes / (GB/s); kept rational: 1 GB/s = 1 byte/ns
     beta_den = max(int(round(gbs)), 1)
     return CostParams(
-        gemm_total=gemm_ns,
+        gemm_total=total,
         comm_bytes=wire_bytes(op, M, N, K, world),
         alpha=calib.publish_ns if fused else calib.launch_ns,
         beta_num=1,
-        beta_den=beta_den,  # 1 GB/s = 1 byte/ns
+        beta_den=beta_den,
         split_overhead=calib.split_ns,
         comm_first=1 if op == "ag_gemm" else 0,
     )

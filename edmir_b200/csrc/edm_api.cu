@@ -17,16 +17,27 @@ using namespace edm;
 namespace {
 
 thread_local int g_last_cuda_error = 0;
-uint64_t g_timeout_ns = 2000ull * 1000ull * 1000ull;
-int g_profile = 0;
+// process-wide settings: written by their setters, read by every launch (relaxed atomics)
+std::atomic<uint64_t> g_timeout_ns{2000ull * 1000ull * 1000ull};
+std::atomic<int> g_profile{0};
+constexpr int kMaxDevices = 64;
 
-// Tuning knobs for experiments, read from the environment once: EDM_STAGE_LIMIT (ring stages),
-// EDM_BAND (row blocks per band of the tile walk), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
+// Index of the current device into the per-device tables below, or -1.
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+// Tuning knobs for experiments, read from the environment once (the operators pass their schedule
+// through edm_tp_call_t, not through these): EDM_STAGE_LIMIT (ring stages),
+// EDM_BAND / EDM_BAND_COLS (row blocks per band of the tile walk / column blocks per super-tile), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
 // shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2),
 // EDM_BLOCK_N (32 or 256: tile width of the single-CTA plain GEMM), EDM_TAIL_SPLIT (most pieces a
 // tile of an incomplete last wave is cut into along K; 0 or 1: none).
 struct Tuning {
-  int stage_limit = 0, band = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0, tail_split = kTailMaxParts;
+  int stage_limit = 0, band = 0, band_cols = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0,
+      tail_split = kTailMaxParts;
   Tuning() {
     auto get = [](const char* name, int dflt) {
       const char* e = std::getenv(name);
@@ -34,6 +45,7 @@ struct Tuning {
     };
     stage_limit = get("EDM_STAGE_LIMIT", 0);
     band = get("EDM_BAND", 0);
+    band_cols = get("EDM_BAND_COLS", 0);
     push_stride = get("EDM_PUSH_STRIDE", 1);
     if (push_stride < 1) push_stride = 1;
     side_streams = get("EDM_SIDE_STREAMS", 2);
@@ -57,12 +69,51 @@ int max_tail_parts(cudaStream_t s) { return capturing(s) ? 0 : tuning().tail_spl
 void apply_tuning(LaunchParams& lp, cudaStream_t s) {
   lp.stage_limit = tuning().stage_limit;
   lp.band = tuning().band;
+  lp.band_cols = tuning().band_cols > 0 ? tuning().band_cols : 0;
   lp.push_stride = tuning().push_stride;
   lp.tail_split = max_tail_parts(s);
   // flags of the split last wave carry a value no earlier launch of this process used
   static std::atomic<uint32_t> tail_epoch{0};
   lp.tail_epoch = tail_epoch.fetch_add(1u) + 1u;
 }
+
+// Checking build (-DEDM_DEBUG_BOUNDS): the entry points collect every range a launch may touch
+// and publish the table to the device before the kernel is enqueued; see tp_gemm.cuh.
+#ifdef EDM_DEBUG_BOUNDS
+struct DbgRanges {
+  unsigned long long lo[kDbgMaxRanges], hi[kDbgMaxRanges];
+  int n = 0;
+  void add(const void* p, size_t bytes) {
+    if (!p || !bytes || n >= kDbgMaxRanges) return;
+    lo[n] = reinterpret_cast<unsigned long long>(p);
+    hi[n] = lo[n] + bytes;
+    ++n;
+  }
+};
+thread_local DbgRanges g_dbg;
+void dbg_reset() { g_dbg.n = 0; }
+void dbg_add(const void* p, size_t bytes) { g_dbg.add(p, bytes); }
+void dbg_add_matrix(const void* p, int64_t rows, int64_t cols, int64_t ld, int elem) {
+  if (rows > 0) g_dbg.add(p, (static_cast<size_t>(rows - 1) * ld + cols) * elem);
+}
+int dbg_publish(cudaStream_t s) {
+  void* p = nullptr;
+  // the library's own device arrays
+  if (cudaGetSymbolAddress(&p, g_tail_scratch) == cudaSuccess) g_dbg.add(p, sizeof(g_tail_scratch));
+  if (cudaGetSymbolAddress(&p, g_tail_flags) == cudaSuccess) g_dbg.add(p, sizeof(g_tail_flags));
+  if (cudaGetSymbolAddress(&p, g_tail_claim) == cudaSuccess) g_dbg.add(p, sizeof(g_tail_claim));
+  if (cudaMemcpyToSymbolAsync(g_dbg_lo, g_dbg.lo, sizeof(unsigned long long) * g_dbg.n, 0, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+      cudaMemcpyToSymbolAsync(g_dbg_hi, g_dbg.hi, sizeof(unsigned long long) * g_dbg.n, 0, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+      cudaMemcpyToSymbolAsync(g_dbg_n, &g_dbg.n, sizeof(int), 0, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return EDM_ERR_CUDA;
+  return cudaStreamSynchronize(s) == cudaSuccess ? EDM_OK : EDM_ERR_CUDA;  // the table is per launch: no overlap in this build
+}
+#else
+inline void dbg_reset() {}
+inline void dbg_add(const void*, size_t) {}
+inline void dbg_add_matrix(const void*, int64_t, int64_t, int64_t, int) {}
+inline int dbg_publish(cudaStream_t) { return EDM_OK; }
+#endif
 
 #define EDM_CUDA(expr)                                   \
   do {                                                   \
@@ -159,20 +210,31 @@ int num_sms() {
 template <int kCG, int kBN, bool kTf32, typename OutT>
 struct Variant {
   static void* fn() { return reinterpret_cast<void*>(&tp_gemm_kernel<kCG, kBN, kTf32, OutT>); }
+  // Function attributes and occupancy belong to a device: one slot per device, filled under a lock
+  // on the first launch there (the attribute call is idempotent, so a race would be harmless, but
+  // the lock also keeps the tables coherent for several host threads).
+  static std::mutex& lock() { static std::mutex m; return m; }
   static int configure() {
-    static bool done = false;
-    if (!done) {
+    static bool done[kMaxDevices] = {};
+    const int dev = current_device();
+    if (dev < 0) return EDM_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> g(lock());
+    if (!done[dev]) {
       EDM_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      done = true;
+      done[dev] = true;
     }
     return EDM_OK;
   }
   // Number of CTAs that can be resident at once (whole pairs for kCG == 2).
   static int max_resident(int sms, int* out) {
-    static int cached = 0;
+    static int per_device[kMaxDevices] = {};
+    const int dev = current_device();
+    if (dev < 0) return EDM_ERR_UNSUPPORTED;
+    int rc = configure();
+    if (rc) return rc;
+    std::lock_guard<std::mutex> g(lock());
+    int& cached = per_device[dev];
     if (!cached) {
-      int rc = configure();
-      if (rc) return rc;
       if (kCG == 1) {
         cached = sms;
       } else {
@@ -218,6 +280,7 @@ struct Variant {
 };
 
 int launch_variant(int dtype, int cg, int bn, const LaunchParams& lp, int grid, bool coop, cudaStream_t stream) {
+  if (int rc = dbg_publish(stream)) return rc;
   if (dtype == EDM_DTYPE_BF16) {
     if (cg == 2) return Variant<2, 256, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
     if (bn == 32) return Variant<1, 32, false, __nv_bfloat16>::launch(lp, grid, coop, stream);
@@ -266,9 +329,19 @@ constexpr int kSegKBlocks = 8;      // 256 K elements per TMEM accumulation segm
 constexpr int kMaxGridCtas = 256;   // upper bound on CTAs of one launch
 constexpr size_t kRunningSumBytes = static_cast<size_t>(kMaxGridCtas) * kBlockM * kBlockN * 4;
 
+// Operand bytes the split needs (tf32 high and low copies of A and B), or 0 when the sum does not
+// fit in `limit` -- evaluated term by term so that extents near 2^30 cannot wrap around.
+size_t split_operand_bytes(int64_t M, int64_t N, int64_t K, size_t limit) {
+  const size_t cap = limit / 8;  // elements of A and B together: 2 copies x 4 bytes each
+  const size_t k = static_cast<size_t>(K);
+  if (k == 0 || static_cast<size_t>(M) > cap / k || static_cast<size_t>(N) > cap / k) return 0;
+  const size_t a_sz = align_up(static_cast<size_t>(M) * k * 4, 256), b_sz = align_up(static_cast<size_t>(N) * k * 4, 256);
+  if (a_sz > limit / 2 || b_sz > limit / 2 - a_sz) return 0;
+  return 2 * (a_sz + b_sz);
+}
 size_t split_ws_bytes(int64_t M, int64_t N, int64_t K) {
-  return 2 * (align_up(static_cast<size_t>(M) * K * 4, 256) + align_up(static_cast<size_t>(N) * K * 4, 256)) +
-         kRunningSumBytes;
+  const size_t ops = split_operand_bytes(M, N, K, static_cast<size_t>(1) << 46);  // 64 TiB: beyond any device
+  return ops ? ops + kRunningSumBytes : 0;
 }
 
 // Fills tmap_a/tmap_b (and runs the tf32 split for fp32) for a GEMM A[M,K] x B[N,K].
@@ -289,7 +362,8 @@ int prepare_operands(RankParams& P, int dtype, int cg, int bn, const void* a, in
   }
   if (dtype != EDM_DTYPE_FP32) return EDM_ERR_BAD_ARG;
   if (K % 4 || N % 4) return EDM_ERR_BAD_ARG;
-  if (!ws || ws_bytes < split_ws_bytes(a_rows, N, K)) return EDM_ERR_CAPACITY;
+  const size_t ws_need = split_ws_bytes(a_rows, N, K);
+  if (!ws || ws_need == 0 || ws_bytes < ws_need) return EDM_ERR_CAPACITY;
   if (reinterpret_cast<uintptr_t>(ws) & 255u) return EDM_ERR_BAD_ARG;
   char* w = static_cast<char*>(ws);
   const size_t a_sz = align_up(static_cast<size_t>(a_rows) * K * 4, 256);
@@ -335,6 +409,7 @@ int grid_for_tiles(int tiles, int cg, int resident, bool may_split, int64_t K, i
 // device.  Two of them on the same stream are ordered anyway; across streams this event keeps them
 // apart (a launch waits for the previous one that was issued on another stream).  Launches under
 // stream capture are left alone: whoever builds the graph orders them.
+// Launches that do not cut any tile (most of them) skip all of this.
 struct ScratchGuard {
   std::mutex mu;
   cudaEvent_t ev = nullptr;
@@ -347,17 +422,29 @@ ScratchGuard* scratch_guard() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   return &guards[dev];
 }
-int scratch_guard_before(cudaStream_t s) {
-  ScratchGuard* g = scratch_guard();
-  if (!g || capturing(s)) return EDM_OK;
+// Would the kernel cut tiles of this launch along K?  Mirrors the condition in tp_gemm_kernel.
+bool launch_splits(const LaunchParams& lp, const RankParams& P, int dtype, int cg, int bn, int grid) {
+  if (dtype != EDM_DTYPE_BF16 || bn != kBlockN || P.passes != 1 || grid > kTailMaxCtas) return false;
+  if (P.mode != kPlain && P.mode != kAG) return false;
+  const int pushers = (P.mode == kAG && P.world > 1 && !P.ag_external) ? lp.pusher_ctas : 0;
+  const int units = (lp.ctas_per_vrank - pushers) / cg;
+  const int64_t tiles = ((static_cast<int64_t>(P.M) + kBlockM * cg - 1) / (kBlockM * cg)) *
+                        ((static_cast<int64_t>(P.N) + bn - 1) / bn);
+  if (tiles > INT32_MAX) return false;
+  const TailSplit split(static_cast<int>(tiles), units, (P.K * 2 + kBlockKBytes - 1) / kBlockKBytes, lp.tail_split);
+  return split.parts > 1;
+}
+// Runs `launch` (which enqueues one kernel on `s`).  When that kernel uses the shared scratch, the
+// lock is held from the wait on the previous user's event until this launch's event is recorded,
+// so two host threads cannot both pass the check and overlap on the GPU.
+template <typename F>
+int launch_with_scratch(bool uses_scratch, cudaStream_t s, F&& launch) {
+  ScratchGuard* g = uses_scratch && !capturing(s) ? scratch_guard() : nullptr;
+  if (!g) return launch();
   std::lock_guard<std::mutex> lock(g->mu);
   if (g->recorded && g->last != s) EDM_CUDA(cudaStreamWaitEvent(s, g->ev, 0));
-  return EDM_OK;
-}
-int scratch_guard_after(cudaStream_t s) {
-  ScratchGuard* g = scratch_guard();
-  if (!g || capturing(s)) return EDM_OK;
-  std::lock_guard<std::mutex> lock(g->mu);
+  const int rc = launch();
+  if (rc) return rc;
   if (!g->ev) EDM_CUDA(cudaEventCreateWithFlags(&g->ev, cudaEventDisableTiming));
   EDM_CUDA(cudaEventRecord(g->ev, s));
   g->last = s;
@@ -373,6 +460,10 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   const int out_bytes = dtype == EDM_DTYPE_BF16 ? 2 : 4;
   if ((reinterpret_cast<uintptr_t>(d) & 15u) || ((ldd * out_bytes) & 15) || ldd < N) return EDM_ERR_BAD_ARG;
   if (lda < K || ldb < K) return EDM_ERR_BAD_ARG;
+  if (dtype == EDM_DTYPE_FP32) {  // before any CUDA call: a bad size must never reach a launch
+    const size_t need = split_ws_bytes(M, N, K);
+    if (!ws || need == 0 || ws_bytes < need) return EDM_ERR_CAPACITY;
+  }
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   RankParams& P = lp.r[0];
@@ -386,6 +477,9 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
   P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
   P.out = d; P.ld_out = ldd;
+  dbg_reset();
+  dbg_add_matrix(d, M, N, ldd, out_bytes);
+  dbg_add(ws, ws_bytes);
   int resident = 0;
   if ((rc = max_resident_ctas(dtype, cg, sms, &resident))) return rc;
   const int tiles = static_cast<int>(((M + kBlockM * cg - 1) / (kBlockM * cg)) * ((N + bn - 1) / bn));
@@ -395,9 +489,8 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
-  if ((rc = scratch_guard_before(s))) return rc;
-  if ((rc = launch_variant(dtype, cg, bn, lp, grid, false, s))) return rc;
-  return scratch_guard_after(s);
+  return launch_with_scratch(launch_splits(lp, P, dtype, cg, bn, grid), s,
+                             [&] { return launch_variant(dtype, cg, bn, lp, grid, false, s); });
 }
 
 }  // namespace
@@ -412,7 +505,6 @@ namespace {
 constexpr size_t kStaticSplitBytes = 8u << 20;
 constexpr int kStaticCtas = 32;
 constexpr size_t kStaticScratchBytes = kStaticSplitBytes + static_cast<size_t>(kStaticCtas) * kBlockM * kBlockN * 4;
-constexpr int kMaxDevices = 64;
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -423,22 +515,24 @@ extern "C" int edm_gemm_fp32_static(const void* a, int64_t lda, const void* b, i
   if (rc) return rc;
   if (K % 4 || N % 4 || lda < K || ldb < K || ldd < N) return EDM_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(d) & 15u) || ((ldd * 4) & 15)) return EDM_ERR_BAD_ARG;
+  // operands too large for the fixed scratch (checked term by term: huge extents must not wrap)
+  if (split_operand_bytes(M, N, K, kStaticSplitBytes) == 0) return EDM_ERR_CAPACITY;
   const size_t a_sz = align_up(static_cast<size_t>(M) * K * 4, 256);
   const size_t b_sz = align_up(static_cast<size_t>(N) * K * 4, 256);
-  if (2 * (a_sz + b_sz) > kStaticSplitBytes) return EDM_ERR_CAPACITY;  // operands too large for the fixed scratch
 
   // Set-up, once per device, with that device current: resolve the device address of the array.
-  static char* scratch_of_device[kMaxDevices] = {};
+  static std::atomic<char*> scratch_of_device[kMaxDevices] = {};
   int dev = 0;
   EDM_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return EDM_ERR_UNSUPPORTED;
-  if (scratch_of_device[dev] == nullptr) {
+  char* w = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (w == nullptr) {
     void* p = nullptr;
     EDM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
     if (p == nullptr) return EDM_ERR_CUDA;
-    scratch_of_device[dev] = static_cast<char*>(p);
+    w = static_cast<char*>(p);
+    scratch_of_device[dev].store(w, std::memory_order_release);  // two threads may both resolve it: same value
   }
-  char* w = scratch_of_device[dev];
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* a_hi = reinterpret_cast<float*>(w);
@@ -460,6 +554,9 @@ extern "C" int edm_gemm_fp32_static(const void* a, int64_t lda, const void* b, i
   P.passes = 3;
   P.seg_kblocks = kSegKBlocks;
   P.scratch = reinterpret_cast<float*>(w + kStaticSplitBytes);  // indexed by CTA: the grid stays <= kStaticCtas
+  dbg_reset();
+  dbg_add_matrix(d, M, N, ldd, 4);
+  dbg_add(w, kStaticScratchBytes);
   P.M = static_cast<int32_t>(M); P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
   P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
   P.out = d; P.ld_out = ldd;
@@ -489,6 +586,7 @@ struct edm_comm {
   static constexpr int kSideStreams = 4;
   cudaStream_t side[kSideStreams] = {};
   cudaEvent_t ev_in = nullptr, ev_out[kSideStreams] = {};
+  int streams_in_use = 0;    // side streams the launch being issued has put copies on
 
   size_t off_flags() const { return 0; }
   size_t off_counters() const { return flag_bytes; }
@@ -564,6 +662,8 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
   P.out = call.d; P.ld_out = call.ldd;
 
   if (W == 1 || call.op == EDM_OP_GEMM) {
+    dbg_add_matrix(call.d, call.M, call.N, call.ldd, out_bytes);
+    dbg_add(call.workspace, call.workspace_bytes);
     // a one-rank group needs no exchange
     if (call.op == EDM_OP_GEMM_AR || call.op == EDM_OP_GEMM_RS || call.op == EDM_OP_GEMM ||
         call.op == EDM_OP_AG_GEMM) {
@@ -601,7 +701,20 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     P.ag_chunks = call.chunks;
     P.ag_local_direct = (rows % kBlockM == 0) ? 1 : 0;
     P.x_local = call.a; P.ld_x = call.lda;
-    P.ag_external = call.transport == EDM_TRANSPORT_COPY_ENGINE ? 1 : 0;
+    // which peers (rank-d, d = 1 .. W-1; d = 0 is the own shard when it is not read in place) get
+    // the shard from copy engines: all, none, or the ce_peers farthest ones
+    const int first_d = P.ag_local_direct ? 1 : 0;
+    if (call.transport == EDM_TRANSPORT_COPY_ENGINE) {
+      P.ag_ce_lo = first_d;
+    } else if (call.transport == EDM_TRANSPORT_HYBRID) {
+      if (call.ce_peers < 0 || call.ce_peers > W - 1) return EDM_ERR_BAD_ARG;
+      P.ag_ce_lo = W - call.ce_peers;
+    } else if (call.transport == EDM_TRANSPORT_SM) {
+      P.ag_ce_lo = W;
+    } else {
+      return EDM_ERR_BAD_ARG;
+    }
+    P.ag_external = P.ag_ce_lo <= first_d ? 1 : 0;
     P.passes = 1;
     // A comes from the local gather buffer [M,K]; the own shard is read in place when it
     // covers whole row blocks
@@ -625,6 +738,11 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     if (rc) return rc;
   }
   c->epoch = epoch;
+  const int64_t a_rows = call.op == EDM_OP_AG_GEMM ? call.M / W : call.M;
+  dbg_add_matrix(call.a, a_rows, call.K, call.lda, elem_bytes);
+  dbg_add_matrix(call.d, call.op == EDM_OP_GEMM_RS ? call.M / W : call.M, call.N, call.ldd, out_bytes);
+  dbg_add(call.workspace, call.workspace_bytes);
+  for (int p = 0; p < W; ++p) dbg_add(c->base[p], c->total_bytes);
   return EDM_OK;
 }
 
@@ -634,7 +752,15 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
 // flag with a stream-ordered 32-bit write, which cannot overtake the copy before it.  No SM takes
 // part, so the GEMM's operand traffic is not disturbed.  `after_launch` closes the bracket: later
 // work on the caller's stream waits until the outgoing copies have read the shard.
-int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) {
+// The caller's stream must have recorded c->ev_in at the point the shard is ready
+// (ag_copy_engine_mark); the copies wait for that event only, so they may be enqueued after the
+// GEMM kernel that consumes them.
+int ag_copy_engine_mark(edm_comm* c, cudaStream_t stream) {
+  EDM_CUDA(cudaEventRecord(c->ev_in, stream));
+  return EDM_OK;
+}
+int ag_copy_engine_issue(edm_comm* c, const RankParams& P, int side_streams, cudaStream_t stream) {
+  (void)stream;
   WriteValue32Fn wv = write_value_fn();
   if (!wv) return EDM_ERR_UNSUPPORTED;
   const int W = P.world;
@@ -642,14 +768,18 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) 
   const int elem = 2;
   const size_t row_bytes = static_cast<size_t>(P.K) * elem;
   const int64_t chunk_rows = (rows + P.ag_chunks - 1) / P.ag_chunks;
-  int nstreams = tuning().side_streams;
+  int nstreams = side_streams > 0 ? side_streams : tuning().side_streams;
   if (nstreams < 1) nstreams = 1;
   if (nstreams > edm_comm::kSideStreams) nstreams = edm_comm::kSideStreams;
-  EDM_CUDA(cudaEventRecord(c->ev_in, stream));
-  for (int i = 0; i < edm_comm::kSideStreams; ++i) EDM_CUDA(cudaStreamWaitEvent(c->side[i], c->ev_in, 0));
+  const int d_lo = P.ag_ce_lo > (P.ag_local_direct ? 1 : 0) ? P.ag_ce_lo : (P.ag_local_direct ? 1 : 0);
+  if (W - d_lo < nstreams) nstreams = W - d_lo > 0 ? W - d_lo : 1;
+  c->streams_in_use = nstreams;
+  for (int i = 0; i < nstreams; ++i) EDM_CUDA(cudaStreamWaitEvent(c->side[i], c->ev_in, 0));
   // when the shard does not cover whole row blocks the kernel also reads the own rows from the
   // gather buffer: deliver them (d = 0) like a peer's
-  for (int d = P.ag_local_direct ? 1 : 0; d < W; ++d) {
+  // every copy must stay inside the half of the peer's window this call uses
+  if (static_cast<size_t>(P.M) * row_bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
+  for (int d = d_lo; d < W; ++d) {
     const int peer = (P.rank - d + W) % W;
     cudaStream_t side = c->side[d % nstreams];
     char* dst0 = static_cast<char*>(P.gather[peer]) + static_cast<size_t>(P.rank) * rows * row_bytes;
@@ -674,7 +804,7 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, cudaStream_t stream) 
   return EDM_OK;
 }
 int ag_copy_engine_after_launch(edm_comm* c, cudaStream_t stream) {
-  for (int i = 0; i < edm_comm::kSideStreams; ++i) {
+  for (int i = 0; i < c->streams_in_use; ++i) {
     EDM_CUDA(cudaEventRecord(c->ev_out[i], c->side[i]));
     EDM_CUDA(cudaStreamWaitEvent(stream, c->ev_out[i], 0));
   }
@@ -706,6 +836,12 @@ int edm_status_clear(void) {
   // a launch that gave up may have left the claim counters of the split last wave part-way
   EDM_CUDA(cudaMemcpyToSymbol(g_tail_next, z, sizeof(uint32_t) * kMaxVirtualRanks));
   return EDM_OK;
+}
+int edm_status_check(void) {
+  uint32_t st[16];
+  const int rc = edm_status_read(st);
+  if (rc) return rc;
+  return st[0] == 0 ? EDM_OK : EDM_ERR_DEVICE_TIMEOUT;
 }
 int edm_profile_enable(int on) {
   g_profile = on ? 1 : 0;
@@ -829,16 +965,23 @@ int edm_comm_heap_reset(edm_comm_t* c) {
   c->heap_used = 0;
   return EDM_OK;
 }
+int edm_comm_poison(edm_comm_t* c, int byte_value, void* stream) {
+  if (!c || !c->base[c->rank]) return EDM_ERR_BAD_ARG;
+  EDM_CUDA(cudaMemsetAsync(c->base[c->rank] + c->off_window(), byte_value & 0xFF, c->window_bytes,
+                           static_cast<cudaStream_t>(stream)));
+  return EDM_OK;
+}
 int edm_comm_rank(const edm_comm_t* c) { return c ? c->rank : -1; }
 int edm_comm_world(const edm_comm_t* c) { return c ? c->world : -1; }
 
 int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m, int tile_n, int band_rows,
-                  int units, int32_t* out, int64_t capacity, int64_t* positions) {
+                  int band_cols, int units, int32_t* out, int64_t capacity, int64_t* positions) {
   if (op < EDM_OP_GEMM || op > EDM_OP_AG_GEMM || world < 1 || world > 8 || rank < 0 || rank >= world || M <= 0 ||
-      N <= 0 || M > INT32_MAX || N > INT32_MAX || tile_m <= 0 || tile_n <= 0 || units < 1 || !positions)
+      N <= 0 || M > INT32_MAX || N > INT32_MAX || tile_m <= 0 || tile_n <= 0 || units < 1 || band_cols < 0 || !positions)
     return EDM_ERR_BAD_ARG;
   const int mode = op == EDM_OP_GEMM ? kPlain : op == EDM_OP_GEMM_RS ? kRS : op == EDM_OP_GEMM_AR ? kAR : kAG;
-  const TileWalk walk(mode, rank, world, static_cast<int>(M), static_cast<int>(N), tile_m, tile_n, band_rows, units);
+  const TileWalk walk(mode, rank, world, static_cast<int>(M), static_cast<int>(N), tile_m, tile_n, band_rows, units,
+                      band_cols);
   if (mode == kRS && world > 1 && walk.mb_per_rank == 0) return EDM_ERR_UNSUPPORTED;
   *positions = walk.positions;
   if (!out) return EDM_OK;
@@ -881,17 +1024,31 @@ int edm_comm_p2p_probe(edm_comm_t* c, int peer, size_t bytes, int mode, void* st
   if (bytes == 0 || bytes % 8192 || bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
-  static bool configured = false;
+  static std::atomic<bool> configured[kMaxDevices] = {};
   const int smem = 8 * 2 * 8192 + 128;
-  if (!configured) {
+  const int dev = current_device();
+  if (dev < 0) return EDM_ERR_UNSUPPORTED;
+  if (!configured[dev].load(std::memory_order_acquire)) {
     EDM_CUDA(cudaFuncSetAttribute(p2p_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   // source: first half of the local window; destination: second half of the peer's
   const char* src = c->base[c->rank] + c->off_window();
   char* dst = c->base[peer] + c->off_window() + c->window_bytes / 2;
   p2p_probe_kernel<<<sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(src, dst, bytes, mode);
   EDM_CUDA(cudaGetLastError());
+  return EDM_OK;
+}
+
+// Dedicated pusher CTAs of an all-gather launch with `per_rank` CTAs per rank: whole pairs, and at
+// least one unit is left for the tiles.  0 when the kernel pushes nothing.
+static int pusher_ctas_for(const edm_tp_call_t& call, const RankParams& P, int cg, int per_rank, int* out) {
+  *out = 0;
+  if (P.mode != kAG || P.world <= 1 || P.ag_external) return EDM_OK;
+  if (call.pusher_ctas < 0) return EDM_ERR_BAD_ARG;
+  const int n = call.pusher_ctas / cg * cg;
+  if (n > per_rank - cg) return EDM_ERR_BAD_ARG;
+  *out = n;
   return EDM_OK;
 }
 
@@ -904,26 +1061,34 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   // would repeat: fused launches cannot be captured
   if (comm->world > 1 && capturing(s)) return EDM_ERR_UNSUPPORTED;
   const int cg = pick_cta_group(call->dtype, call->op, call->M, comm->world);
+  dbg_reset();
   int rc = build_rank_params(comm, *call, cg, lp.r[0], s);
   if (rc) return rc;
+  const RankParams& P = lp.r[0];
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
   int resident = 0;
   if ((rc = max_resident_ctas(call->dtype, cg, sms, &resident))) return rc;
-  const int grid = grid_for(lp.r[0], cg, resident);
+  const int grid = grid_for(P, cg, resident);
   lp.num_vranks = 1;
   lp.ctas_per_vrank = grid;
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   apply_tuning(lp, s);
-  const bool ce = lp.r[0].mode == kAG && lp.r[0].ag_external;
-  if (ce && (rc = ag_copy_engine_issue(comm, lp.r[0], s))) return rc;
-  const bool may_split = lp.r[0].mode == kAG;  // the only fused mode that writes its tiles in place
-  if (may_split && (rc = scratch_guard_before(s))) return rc;
-  rc = launch_variant(call->dtype, cg, kBlockN, lp, grid, false, s);
+  if (call->band_rows > 0) lp.band = call->band_rows;
+  if (call->band_cols > 0) lp.band_cols = call->band_cols;
+  if ((rc = pusher_ctas_for(*call, P, cg, grid, &lp.pusher_ctas))) return rc;
+  const bool ce = P.mode == kAG && P.world > 1 && P.ag_ce_lo < P.world;
+  // the kernel goes first (it starts on this rank's own shard); the copies only wait for the
+  // point on the caller's stream where the shard was ready
+  if (ce && (rc = ag_copy_engine_mark(comm, s))) return rc;
+  rc = launch_with_scratch(launch_splits(lp, P, call->dtype, cg, kBlockN, grid), s,
+                           [&] { return launch_variant(call->dtype, cg, kBlockN, lp, grid, false, s); });
   if (rc) return rc;
-  if (may_split && (rc = scratch_guard_after(s))) return rc;
-  if (ce) return ag_copy_engine_after_launch(comm, s);
+  if (ce) {
+    if ((rc = ag_copy_engine_issue(comm, P, call->side_streams, s))) return rc;
+    return ag_copy_engine_after_launch(comm, s);
+  }
   return EDM_OK;
 }
 
@@ -934,9 +1099,11 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (capturing(s)) return EDM_ERR_UNSUPPORTED;  // see edm_tp_launch
   const int cg = pick_cta_group(calls[0].dtype, calls[0].op, calls[0].M, comms[0] ? comms[0]->world : 1);
+  dbg_reset();
   for (int i = 0; i < n; ++i) {
     if (!comms[i] || calls[i].dtype != calls[0].dtype || calls[i].op != calls[0].op ||
-        calls[i].M != calls[0].M)
+        calls[i].M != calls[0].M || calls[i].pusher_ctas != calls[0].pusher_ctas ||
+        calls[i].band_rows != calls[0].band_rows || calls[i].band_cols != calls[0].band_cols)
       return EDM_ERR_BAD_ARG;
     int rc = build_rank_params(comms[i], calls[i], cg, lp.r[i], s);
     if (rc) return rc;
@@ -953,15 +1120,27 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   lp.timeout_ns = g_timeout_ns;
   lp.profile = g_profile;
   apply_tuning(lp, s);
-  for (int i = 0; i < n; ++i)
-    if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_issue(comms[i], lp.r[i], s))) return rc;
-  if ((rc = scratch_guard_before(s))) return rc;
-  rc = launch_variant(calls[0].dtype, cg, kBlockN, lp, lp.ctas_per_vrank * n, true, s);
-  if (rc) return rc;
-  if ((rc = scratch_guard_after(s))) return rc;
-  for (int i = 0; i < n; ++i)
-    if (lp.r[i].mode == kAG && lp.r[i].ag_external && (rc = ag_copy_engine_after_launch(comms[i], s))) return rc;
-  return EDM_OK;
+  if (calls[0].band_rows > 0) lp.band = calls[0].band_rows;
+  if (calls[0].band_cols > 0) lp.band_cols = calls[0].band_cols;
+  if ((rc = pusher_ctas_for(calls[0], lp.r[0], cg, lp.ctas_per_vrank, &lp.pusher_ctas))) return rc;
+  // Copies between buffers of ONE device may be carried out by kernels, which cannot start while
+  // the cooperative launch holds every SM (a chunked copy would then starve behind it until the
+  // kernel's waits run out).  The emulation therefore lets the copies finish first: the kernel
+  // still finds its rows through the chunk flags and the gather buffer, only the overlap -- which
+  // a single device cannot show anyway -- is given up.
+  bool splits = false;
+  for (int i = 0; i < n; ++i) {
+    const RankParams& P = lp.r[i];
+    splits = splits || launch_splits(lp, P, calls[0].dtype, cg, kBlockN, lp.ctas_per_vrank * n);
+    if (P.mode == kAG && P.world > 1 && P.ag_ce_lo < P.world) {
+      if ((rc = ag_copy_engine_mark(comms[i], s))) return rc;
+      if ((rc = ag_copy_engine_issue(comms[i], P, calls[i].side_streams, s))) return rc;
+      if ((rc = ag_copy_engine_after_launch(comms[i], s))) return rc;
+    }
+  }
+  return launch_with_scratch(splits, s, [&] {
+    return launch_variant(calls[0].dtype, cg, kBlockN, lp, lp.ctas_per_vrank * n, true, s);
+  });
 }
 
 static int tp_bf16(edm_comm_t* comm, int op, const void* a, int64_t lda, const void* b, int64_t ldb,

@@ -31,6 +31,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// Counts `bytes` as transferred on the barrier (stands in for a copy that was not issued).
+__device__ __forceinline__ void mbar_complete_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -115,6 +119,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src_glo
 template <int N>
 __device__ __forceinline__ void bulk_wait_pending() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Wait until at most N of this thread's most recent bulk groups are still reading their source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read_pending() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() {

@@ -69,6 +69,7 @@ enum Status : uint32_t {
   kTimeoutResultFlag = 6,    // AR: an owner's reduced tile never arrived
   kTimeoutGatherFlag = 7,    // AG: a peer's shard chunk never arrived
   kTimeoutTailFlag = 8,      // split last wave: another CTA's partial sum never arrived
+  kBoundsFault = 9,          // checking build only: an address outside every range the launch may touch
 };
 
 __device__ uint32_t g_status[16];
@@ -114,6 +115,7 @@ struct alignas(64) RankParams {
   float* scratch;          // split-fp32: running fp32 sums, one kBlockM x kBlockN tile per CTA
   int32_t seg_kblocks;     // split-fp32: K blocks accumulated in TMEM before folding into scratch (0 = all)
   int32_t ag_external;     // AG: shards and chunk flags are delivered by copy engines, not by this kernel
+  int32_t ag_ce_lo;        // AG: shards for peers rank-d with d >= ag_ce_lo come by copy engine, nearer ones are pushed by this kernel
   void* peer_out[kMaxRanks];   // AR: every rank's output as mapped here
   char* win[kMaxRanks];        // every rank's window (parity half already selected)
   uint32_t* flags[kMaxRanks];  // every rank's flag array
@@ -128,6 +130,8 @@ struct LaunchParams {
   int32_t stage_limit;    // experiments: use at most this many ring stages (0 = all)
   int32_t push_stride;    // all-gather: only CTAs whose index is a multiple of this push the shard
   int32_t band;           // row blocks per band of the tile walk (0 = default)
+  int32_t band_cols;      // column blocks per super-tile of a band (0 = the whole width)
+  int32_t pusher_ctas;    // all-gather: the last CTAs of every rank only push the shard (no tiles); 0 = push warps inside the GEMM CTAs
   int32_t tail_split;     // most pieces a tile of an incomplete last wave is cut into along K (< 2: none)
   uint32_t tail_epoch;    // value the partial-sum flags of this launch carry
   RankParams r[kMaxVirtualRanks];
@@ -148,42 +152,74 @@ __device__ __forceinline__ bool aborted() {
   return *reinterpret_cast<volatile uint32_t*>(&g_status[0]) != 0u;
 }
 
+// ------------------------------------------------------------------ checking build
+// Compiled with -DEDM_DEBUG_BOUNDS every global-memory address the kernel computes itself (output
+// and window stores, bulk copies, flag words, scratch tiles; TMA loads are bounded by their tensor
+// maps) is looked up in a table of the ranges the launch may touch, which the host fills before
+// the launch.  An address outside all of them is recorded in the status words
+// {kBoundsFault, CTA, thread, site, address high, address low} and the access is skipped, so a
+// wrong index shows up as a status code instead of a fault.  The ordinary build compiles the
+// checks away.
+#ifdef EDM_DEBUG_BOUNDS
+constexpr int kDbgMaxRanges = 64;
+__device__ unsigned long long g_dbg_lo[kDbgMaxRanges], g_dbg_hi[kDbgMaxRanges];
+__device__ int g_dbg_n;
+__device__ __noinline__ bool addr_ok(const void* p, size_t n, uint32_t site) {
+  const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+  for (int i = 0; i < g_dbg_n; ++i)
+    if (a >= g_dbg_lo[i] && a + n <= g_dbg_hi[i]) return true;
+  report(kBoundsFault, site, static_cast<uint32_t>(a >> 32), static_cast<uint32_t>(a));
+  return false;
+}
+#define EDM_ADDR_OK(p, n, site) addr_ok((p), (n), (site))
+#else
+#define EDM_ADDR_OK(p, n, site) true
+#endif
+
 // prof_slot >= 0: add the time spent here to that accounting slot (only the slow path pays for it)
-__device__ __noinline__ void wait_mbar_slow(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
+// Both waits return true when what they waited for has happened and false when they gave up
+// (their own limit ran out, or another wait anywhere on the device already had).  A role that gets
+// false stops issuing work -- no further loads, MMAs or copies -- and goes to the tear-down, so
+// that what is still in flight when the CTA exits is bounded by what the pipeline normally holds.
+__device__ __noinline__ bool wait_mbar_slow(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
                                             uint32_t code, uint32_t info, int prof_slot) {
   const uint64_t start = prof_slot >= 0 ? globaltimer_ns() : 0;
   uint64_t t0 = 0;
   uint32_t spins = 0;
+  bool ok = true;
   while (!mbar_try_wait(bar, parity)) {
     if ((spins++ & 15u) == 0u) {
-      if (aborted()) break;
+      if (aborted()) { ok = false; break; }
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > timeout_ns) { report(code, info, parity, bar); break; }
+      else if (now - t0 > timeout_ns) { report(code, info, parity, bar); ok = false; break; }
     }
   }
   if (prof_slot >= 0) atomicAdd(&g_prof[prof_slot], static_cast<unsigned long long>(globaltimer_ns() - start));
+  return ok;
 }
-__device__ __forceinline__ void wait_mbar(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
+__device__ __forceinline__ bool wait_mbar(uint32_t bar, uint32_t parity, uint64_t timeout_ns,
                                           uint32_t code, uint32_t info, int prof_slot = -1) {
-  if (mbar_try_wait(bar, parity)) return;
-  wait_mbar_slow(bar, parity, timeout_ns, code, info, prof_slot);
+  if (mbar_try_wait(bar, parity)) return true;
+  return wait_mbar_slow(bar, parity, timeout_ns, code, info, prof_slot);
 }
 
 // Wait until *flag (written by another GPU / CTA with release.sys) has reached `epoch`.
-__device__ __noinline__ void wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
+__device__ __noinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
                                        uint32_t code, uint32_t info) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
+  if (!EDM_ADDR_OK(flag, 4, 1u)) return false;
   while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
     if ((spins++ & 31u) == 0u) {
-      if (aborted()) return;
+      if (aborted()) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > timeout_ns) { report(code, info, epoch, ld_relaxed_sys(flag)); return; }
+      else if (now - t0 > timeout_ns) { report(code, info, epoch, ld_relaxed_sys(flag)); return false; }
     }
     __nanosleep(64);
   }
+  return true;
 }
 
 // ------------------------------------------------------------------ tile enumeration
@@ -197,14 +233,26 @@ struct Tile {
 
 // Walk an (mb x nb) grid in bands of kBand row-blocks so that concurrently running CTAs share
 // A and B panels in L2 (taller bands re-read B less often; 16 measured best on the layer's shapes).
-__host__ __device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n, int kBand = 8) {
+// With kCols > 0 a band is further cut into super-tiles of kCols column blocks that are finished one
+// after the other: the tiles in flight at any time then cover about kBand x kCols blocks, i.e.
+// kBand panels of A and kCols panels of B, instead of kBand panels of A and a sliver of B.
+__host__ __device__ __forceinline__ void band_order(int i, int mb, int nb, int& m, int& n, int kBand = 8,
+                                                    int kCols = 0) {
   const int per_band = kBand * nb;
   const int band = i / per_band;
   const int first = band * kBand;
   const int rows = min(kBand, mb - first);
   const int j = i - band * per_band;
-  m = first + j % rows;
-  n = j / rows;
+  if (kCols <= 0 || kCols >= nb) {
+    m = first + j % rows;
+    n = j / rows;
+    return;
+  }
+  const int per_super = rows * kCols;  // every super-tile before the last one of a band is full
+  const int sup = j / per_super;
+  const int jj = j - sup * per_super;
+  m = first + jj % rows;
+  n = sup * kCols + jj / rows;
 }
 
 struct TileWalk {
@@ -213,18 +261,20 @@ struct TileWalk {
   int positions;    // length of the walk (>= total when it has holes)
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
   int band;         // row blocks per band of the walk
+  int band_cols;    // column blocks per super-tile of a band (0: the whole width)
   int ag_head_blocks, ag_head_band;  // all-gather: the first row blocks are walked in lower bands
   int rounds;       // RS/AR: rounds of the owner round-robin (= most tiles any rank owns)
   int defer;        // RS/AR: own tiles of the last `defer` rounds are computed at the very end
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
   // units = CTAs (or CTA pairs) walking the tiles concurrently
-  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units)
-      : TileWalk(p.mode, p.rank, p.world, p.M, p.N, tile_m, tile_n, band_rows, units) {}
+  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units, int cols)
+      : TileWalk(p.mode, p.rank, p.world, p.M, p.N, tile_m, tile_n, band_rows, units, cols) {}
   __host__ __device__ TileWalk(int mode_, int rank_, int world_, int M, int N, int tile_m, int tile_n,
-                               int band_rows, int units) {
+                               int band_rows, int units, int cols = 0) {
     mode = mode_; rank = rank_; world = world_;
     band = band_rows > 0 ? band_rows : 16;  // 16 x 256 rows of A stay in L2 while B streams through once per band
+    band_cols = cols > 0 ? cols : 0;
     m_blocks = (M + tile_m - 1) / tile_m;
     n_blocks = (N + tile_n - 1) / tile_n;
     total = m_blocks * n_blocks;
@@ -295,7 +345,7 @@ struct TileWalk {
       if (i < head_tiles) {
         band_order(i, ag_head_blocks, n_blocks, pm, n, ag_head_band);
       } else {
-        band_order(i - head_tiles, m_blocks - ag_head_blocks, n_blocks, pm, n, band);
+        band_order(i - head_tiles, m_blocks - ag_head_blocks, n_blocks, pm, n, band, band_cols);
         pm += ag_head_blocks;
       }
       t.m_blk = (rank * mb_per_rank + pm) % m_blocks;  // own shard first, then rank+1, ...
@@ -303,7 +353,7 @@ struct TileWalk {
       t.owner = rank;
       t.owned_idx = 0;
     } else {
-      band_order(i, m_blocks, n_blocks, t.m_blk, t.n_blk, band);
+      band_order(i, m_blocks, n_blocks, t.m_blk, t.n_blk, band, band_cols);
       t.owner = rank;
       t.owned_idx = 0;
     }
@@ -491,11 +541,16 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 
   const int vr = blockIdx.x / lp.ctas_per_vrank;
   const int cta_in_rank = blockIdx.x - vr * lp.ctas_per_vrank;
+  const RankParams& P = lp.r[vr];
+  // all-gather with dedicated pushers: the last pusher_ctas CTAs (whole pairs) of every rank take
+  // no tiles; they only move this rank's shard into the peers' gather buffers
+  const int pusher_ctas = (P.mode == kAG && P.world > 1 && !P.ag_external) ? lp.pusher_ctas : 0;
+  const int gemm_ctas = lp.ctas_per_vrank - pusher_ctas;
+  const bool is_pusher = cta_in_rank >= gemm_ctas;
   // scheduling unit: a CTA, or a CTA pair (ctas_per_vrank is even then and pairs never straddle ranks)
   const int cta = cta_in_rank / kCG;
-  const int num_ctas = lp.ctas_per_vrank / kCG;
+  const int num_ctas = gemm_ctas / kCG;
   const uint32_t pr = kCG == 2 ? cluster_ctarank() : 0u;  // position in the pair; 0 issues the MMAs
-  const RankParams& P = lp.r[vr];
   const uint64_t timeout_ns = lp.timeout_ns;
   const bool prof = lp.profile != 0;
   ProfTimer prof_kernel(prof && threadIdx.x == 0);
@@ -511,7 +566,12 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
   const uint32_t bar_tail = smem_u32(&bars[2 * kMaxStages + 4]);  // one per epilogue warp: partial sums have landed
   // all-gather with the sm transport: warps 2, 3 and 9-11 push this rank's shard to the peers
-  const bool ag_push = P.mode == kAG && P.world > 1 && !P.ag_external;
+  const bool ag_push = P.mode == kAG && P.world > 1 && !P.ag_external && pusher_ctas == 0;
+  constexpr int kPusherWarps = 6;        // warps of a pusher CTA that drive copies (one lane each)
+  constexpr int kPushDepth = 4;          // staging buffers per such warp
+  constexpr uint32_t kPushBytes = 8192;  // bytes per copy: kPusherWarps * kPushDepth * kPushBytes = the operand ring
+  static_assert(kPusherWarps * kPushDepth * kPushBytes <= kPipeBytes, "pusher staging exceeds the ring");
+  static_assert(kPusherWarps * kPushDepth <= 2 * kMaxStages + 8, "not enough barriers for the pusher staging");
   uint32_t stages = kStages;
   if (lp.stage_limit > 0 && static_cast<uint32_t>(lp.stage_limit) < stages) stages = lp.stage_limit;
 
@@ -520,19 +580,24 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     mbox[threadIdx.x].ready = 0; mbox[threadIdx.x].done = 0; mbox[threadIdx.x].closed = 0;
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
+    if (is_pusher) {
+      // one barrier per staging buffer: a local bulk load has landed
+      for (int i = 0; i < kPusherWarps * kPushDepth; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    } else {
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(bar_full + 8 * s, 1);
+        mbar_init(bar_empty + 8 * s, 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(bar_tfull + 8 * a, 1);
+        mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
+      }
+      for (int w = 0; w < 4; ++w) mbar_init(bar_tail + 8 * w, 1);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 4 * kCG);  // every epilogue warp of the pair
-    }
-    for (int w = 0; w < 4; ++w) mbar_init(bar_tail + 8 * w, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (warp == 2) {
+  if (warp == 2 && !is_pusher) {
     tmem_alloc<kCG>(smem_u32(&tmem_base_slot), kTmemCols);
     tmem_relinquish<kCG>();
   }
@@ -542,7 +607,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P, kBlockM * kCG, kBN, lp.band, num_ctas);
+  const TileWalk walk(P, kBlockM * kCG, kBN, lp.band, num_ctas, lp.band_cols);
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -565,8 +630,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     const uint32_t got = atomicAdd(&g_tail_next[vr], 1u);
     // every unit claims exactly once per launch: the last one leaves the counter at zero
     if (got == static_cast<uint32_t>(num_ctas) - 1u) atomicExch(&g_tail_next[vr], 0u);
-    *reinterpret_cast<volatile unsigned long long*>(&g_tail_claim[first_cta_of_unit]) =
-        (static_cast<unsigned long long>(lp.tail_epoch) << 32) | got;
+    if (EDM_ADDR_OK(&g_tail_claim[first_cta_of_unit], 8, 19u))
+      *reinterpret_cast<volatile unsigned long long*>(&g_tail_claim[first_cta_of_unit]) =
+          (static_cast<unsigned long long>(lp.tail_epoch) << 32) | got;
     return static_cast<int>(got);
   };
   auto await_piece = [&]() -> int {
@@ -625,9 +691,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     const int64_t dst_ld = static_cast<int64_t>(P.K) * kElemBytes;
     const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
     const int first_d = P.ag_local_direct ? 1 : 0;
+    const int d_hi = min(P.world, P.ag_ce_lo);  // farther peers get the shard from copy engines
     // peer-major: the whole shard goes to rank-1 first (it consumes this shard right after its
     // own), then to rank-2, ...: every GPU sends to and receives from one peer at a time
-    for (int d = first_d; d < P.world; ++d) {
+    for (int d = first_d; d < d_hi; ++d) {
       const int peer = (P.rank - d + P.world) % P.world;
       const char* src = static_cast<const char*>(P.x_local);
       char* dst = static_cast<char*>(P.gather[peer]);
@@ -644,7 +711,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             const int64_t v = v0 + u * 32 + lane;
             if (v < nvec) {
               const int64_t row = v / row_vecs, col = v - row * row_vecs;
-              buf[u] = ld_cg_v4(src + (r_lo + row) * src_ld + col * 16);
+              if (EDM_ADDR_OK(src + (r_lo + row) * src_ld + col * 16, 16, 2u))
+                buf[u] = ld_cg_v4(src + (r_lo + row) * src_ld + col * 16);
             }
           }
 #pragma unroll
@@ -652,7 +720,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             const int64_t v = v0 + u * 32 + lane;
             if (v < nvec) {
               const int64_t row = v / row_vecs, col = v - row * row_vecs;
-              st_global_v4(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, buf[u]);
+              if (EDM_ADDR_OK(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, 16, 3u))
+                st_global_v4(dst + (dst_row0 + r_lo + row) * dst_ld + col * 16, buf[u]);
             }
           }
         }
@@ -693,12 +762,14 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       const int64_t src_stride = static_cast<int64_t>(P.max_owned) * kTileOutBytes;
       {
         ProfTimer rf(rprof);
+        bool arrived = true;
         if (lane < W)
-          wait_flag(P.flags[P.rank] + P.partial_flag_off +
-                        (static_cast<uint32_t>(lane) * P.max_owned + item) * 4 + qq,
-                    P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | item);
-        __syncwarp();
+          arrived = wait_flag(P.flags[P.rank] + P.partial_flag_off +
+                                  (static_cast<uint32_t>(lane) * P.max_owned + item) * 4 + qq,
+                              P.epoch, timeout_ns, kTimeoutPartialFlag, (lane << 24) | item);
+        arrived = __all_sync(0xffffffffu, arrived);
         rf.stop(kProfReducerFlagWait);
+        if (!arrived) return;  // a partial never came: nothing more to add up in this launch
 #pragma unroll 1
         for (int h = 0; h < kPasses; ++h) {
           const char* blk = slot0 + (h * 4 + qq) * kEpiWarpBytes;  // 512 vectors of 16 B
@@ -715,7 +786,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
               for (int u = 0; u < kU; ++u)
 #pragma unroll
                 for (int src = 0; src < kW; ++src)
-                  x[u][src] = ld_cg_v4(blk + src * src_stride + ((it + u) * 32 + lane) * 16);
+                  x[u][src] = EDM_ADDR_OK(blk + src * src_stride + ((it + u) * 32 + lane) * 16, 16, 4u)
+                                  ? ld_cg_v4(blk + src * src_stride + ((it + u) * 32 + lane) * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
               for (int u = 0; u < kU; ++u) {
                 float sum[kOutPerVec];
@@ -744,11 +816,13 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                 if (trow < valid_rows && col < valid_cols) {
                   const int64_t off = (out_row0 + trow) * ld_bytes + static_cast<int64_t>(n0 + col) * kOutBytes;
                   if (P.mode == kRS) {
-                    st_global_v4(static_cast<char*>(P.out) + off, o);
+                    if (EDM_ADDR_OK(static_cast<char*>(P.out) + off, 16, 5u))
+                      st_global_v4(static_cast<char*>(P.out) + off, o);
                   } else {
 #pragma unroll
                     for (int d = 0; d < kW; ++d)
-                      st_global_v4(static_cast<char*>(P.peer_out[(P.rank + d) % kW]) + off, o);
+                      if (EDM_ADDR_OK(static_cast<char*>(P.peer_out[(P.rank + d) % kW]) + off, 16, 6u))
+                        st_global_v4(static_cast<char*>(P.peer_out[(P.rank + d) % kW]) + off, o);
                   }
                 }
               }
@@ -777,7 +851,192 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     }
   };
 
-  if (warp == 0) {
+  // ------------------------------------------------------------------ dedicated pusher CTAs
+  // One lane of each of kPusherWarps warps moves 8 KiB segments of the shard: bulk load from local
+  // memory into one of its kPushDepth staging buffers, bulk store from there into the peer's gather
+  // buffer.  Loads run kPushDepth - 1 segments ahead of the stores.  Segments are dealt round-robin
+  // over all pusher warps of the rank; a warp posts one note per (peer, chunk) -- also when it
+  // moved nothing of it -- once its copies of that chunk have been written, and the signaller that
+  // counts the last note raises the chunk's flag at the peer.  Waiting for "written" right after
+  // the last copy of a chunk would drain the warp's pipeline, so the note goes out kPushDepth
+  // segments later, when the bulk-group count alone proves the chunk's copies complete.
+  auto pusher_role = [&](int w) {
+    if (lane != 0) return;
+    ProfTimer push_total(prof && w == 0);
+    const int T = pusher_ctas * kPusherWarps;
+    const int gw = (cta_in_rank - gemm_ctas) * kPusherWarps + w;
+    const int first_d = P.ag_local_direct ? 1 : 0;
+    const int d_hi = min(P.world, P.ag_ce_lo);
+    const int chunk_rows = (rows_per_rank + P.ag_chunks - 1) / P.ag_chunks;
+    const int64_t row_bytes = static_cast<int64_t>(P.K) * kElemBytes;
+    const int64_t src_ld = P.ld_x * kElemBytes;
+    const bool flat = src_ld == row_bytes;  // contiguous shard: segments ignore row boundaries
+    const int64_t segs_per_row = (row_bytes + kPushBytes - 1) / kPushBytes;
+    const int64_t dst_row0 = static_cast<int64_t>(P.rank) * rows_per_rank;
+    const uint32_t buf0 = smem_base + static_cast<uint32_t>(w) * kPushDepth * kPushBytes;
+    const uint32_t bar0 = smem_u32(&bars[w * kPushDepth]);
+
+    struct Cursor { int d, c, r_lo, r_hi; int64_t s, nseg, rot; };
+    auto open_chunk = [&](Cursor& u) {
+      u.r_lo = u.c * chunk_rows;
+      u.r_hi = min(u.r_lo + chunk_rows, rows_per_rank);
+      const int64_t rows = max(u.r_hi - u.r_lo, 0);
+      u.nseg = flat ? (rows * row_bytes + kPushBytes - 1) / kPushBytes : rows * segs_per_row;
+      u.s = ((gw - u.rot) % T + T) % T;  // continues the round-robin where the previous chunk stopped
+    };
+    // next item of this warp's sequence: 0 = a segment, 1 = a chunk is finished (note), 2 = the end
+    auto advance = [&](Cursor& u, const char*& src, char*& dst, uint32_t& bytes, uint64_t& note) -> int {
+      if (u.d >= d_hi) return 2;
+      const int peer = (P.rank - u.d + P.world) % P.world;
+      if (u.s < u.nseg) {
+        int64_t so, dof;
+        if (flat) {
+          const int64_t off = u.s * kPushBytes, total = static_cast<int64_t>(u.r_hi - u.r_lo) * row_bytes;
+          bytes = static_cast<uint32_t>(min(static_cast<int64_t>(kPushBytes), total - off));
+          so = u.r_lo * row_bytes + off;
+          dof = (dst_row0 + u.r_lo) * row_bytes + off;
+        } else {
+          const int64_t row = u.s / segs_per_row, off = (u.s - row * segs_per_row) * kPushBytes;
+          bytes = static_cast<uint32_t>(min(static_cast<int64_t>(kPushBytes), row_bytes - off));
+          so = (u.r_lo + row) * src_ld + off;
+          dof = (dst_row0 + u.r_lo + row) * row_bytes + off;
+        }
+        src = static_cast<const char*>(P.x_local) + so;
+        dst = static_cast<char*>(P.gather[peer]) + dof;
+        u.s += T;
+        return 0;
+      }
+      note = make_note(kNoteChunk, (static_cast<uint64_t>(peer) << 24) | static_cast<uint64_t>(u.c));
+      u.rot = (u.rot + u.nseg) % T;
+      if (++u.c == P.ag_chunks) { u.c = 0; ++u.d; }
+      if (u.d < d_hi) open_chunk(u);
+      return 1;
+    };
+
+    Cursor lc{first_d, 0, 0, 0, 0, 0, 0};
+    if (first_d < d_hi) open_chunk(lc);
+    Cursor sc = lc;
+    uint32_t loads = 0, stores = 0;  // segments whose load / store has been issued
+    auto issue_load = [&]() -> bool {
+      const char* src = nullptr; char* dst = nullptr; uint32_t bytes = 0; uint64_t note = 0;
+      int k;
+      while ((k = advance(lc, src, dst, bytes, note)) == 1) {}
+      if (k == 2) return false;
+      const uint32_t b = loads % kPushDepth;
+      mbar_arrive_expect_tx(bar0 + 8 * b, bytes);
+      if (EDM_ADDR_OK(src, bytes, 7u)) bulk_load(buf0 + b * kPushBytes, src, bytes, bar0 + 8 * b);
+      else mbar_complete_tx(bar0 + 8 * b, bytes);  // checking build: keep the barrier's byte count whole
+      ++loads;
+      return true;
+    };
+    for (int i = 0; i < kPushDepth - 1; ++i)
+      if (!issue_load()) break;
+    bool pending = false;  // a finished chunk whose note has not been posted yet
+    uint64_t pending_note = 0;
+    uint32_t since = 0;    // copies issued since that chunk ended
+    while (true) {
+      const char* src = nullptr; char* dst = nullptr; uint32_t bytes = 0; uint64_t note = 0;
+      const int k = advance(sc, src, dst, bytes, note);
+      if (k == 2) break;
+      if (k == 1) {
+        if (pending) {
+          bulk_wait_pending<0>();
+          mailbox_post(&mbox[w], pending_note, timeout_ns);
+        }
+        pending = true; pending_note = note; since = 0;
+        continue;
+      }
+      const uint32_t b = stores % kPushDepth;
+      if (!wait_mbar(bar0 + 8 * b, (stores / kPushDepth) & 1u, timeout_ns, kTimeoutFullBar,
+                     0x8000u | static_cast<uint32_t>(w)))
+        break;  // a local load never landed: stop copying (what is in flight is awaited below)
+      if (EDM_ADDR_OK(dst, bytes, 8u)) bulk_store(dst, buf0 + b * kPushBytes, bytes);
+      bulk_commit();
+      ++stores;
+      // the load that runs kPushDepth - 1 ahead reuses the buffer of the previous store: wait
+      // until that store has read it
+      bulk_wait_read_pending<1>();
+      issue_load();
+      if (pending && ++since >= static_cast<uint32_t>(kPushDepth)) {
+        bulk_wait_pending<kPushDepth>();  // everything older than the last kPushDepth copies is written
+        mailbox_post(&mbox[w], pending_note, timeout_ns);
+        pending = false;
+      }
+    }
+    bulk_wait_pending<0>();
+    if (pending && !aborted()) mailbox_post(&mbox[w], pending_note, timeout_ns);
+    push_total.stop(kProfPushTotal);
+  };
+
+  // ------------------------------------------------------------------ signaller
+  // Lane w serves mailbox w.  A batch of notes costs one system-scope fence; the flag stores
+  // after it are relaxed (the fence already orders the landed data before them).
+  auto signaller_role = [&]() {
+    // (nothing is ever posted without an exchange, nor by the tile CTAs of a launch with dedicated
+    // pushers: stay off the issue slots then)
+    if (lane < kMailboxes && P.world > 1 && P.mode != kPlain && !(P.mode == kAG && P.ag_external) &&
+        !(pusher_ctas > 0 && !is_pusher)) {
+      volatile Mailbox* mb = &mbox[lane];
+      uint32_t done = 0;
+      uint64_t idle_since = 0;
+      const int total_push_warps = pusher_ctas > 0 ? pusher_ctas * kPusherWarps
+          : (lp.ctas_per_vrank + max(lp.push_stride, 1) - 1) / max(lp.push_stride, 1) * kPushWarps;
+      while (true) {
+        const uint32_t ready = mb->ready;
+        if (ready != done) {
+          __threadfence_block();
+          fence_acq_rel_sys();
+          for (; done != ready; ++done) {
+            const uint64_t note = mb->note[done % kMailboxDepth];
+            const uint64_t kind = note >> 60, payload = note & ((1ull << 60) - 1);
+            if (kind == kNoteFlag) {
+              if (EDM_ADDR_OK(reinterpret_cast<uint32_t*>(payload), 4, 9u))
+                st_relaxed_sys(reinterpret_cast<uint32_t*>(payload), P.epoch);
+            } else if (kind == kNoteResult) {
+              for (int peer = 0; peer < P.world; ++peer)
+                if (peer != P.rank && EDM_ADDR_OK(P.flags[peer] + P.result_flag_off + static_cast<uint32_t>(payload), 4, 10u))
+                  st_relaxed_sys(P.flags[peer] + P.result_flag_off + static_cast<uint32_t>(payload), P.epoch);
+            } else {
+              const int peer = static_cast<int>(payload >> 24), c = static_cast<int>(payload & 0xFFFFFF);
+              uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
+              if (!EDM_ADDR_OK(ctr, 4, 11u) ||
+                  !EDM_ADDR_OK(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, 4, 12u)) continue;
+              if (atomicAdd(ctr, 1u) == static_cast<uint32_t>(total_push_warps - 1)) {
+                // last push warp of this GPU: every piece of the chunk has been written
+                *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;
+                fence_acq_rel_sys();
+                st_relaxed_sys(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, P.epoch);
+              }
+            }
+          }
+          mb->done = done;
+          idle_since = 0;
+        } else if (mb->closed) {
+          if (mb->ready == done) break;
+        } else {
+          __nanosleep(1000);
+          if (aborted()) break;
+          const uint64_t now = globaltimer_ns();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > 4 * timeout_ns) break;  // posters are bounded; this is a backstop
+        }
+      }
+    }
+  };
+
+  if (is_pusher) {
+    // ============================ pusher CTA ============================
+    if (warp < kPusherWarps) {
+      pusher_role(warp);
+      if (lane == 0) mailbox_close(&mbox[warp]);
+    } else if (warp == 8) {
+      signaller_role();
+    } else if (lane == 0) {
+      // mailboxes nobody posts to: warps 6, 7 close theirs, warp 9 closes the last one
+      if (warp < 8) mailbox_close(&mbox[warp]);
+      else if (warp == 9) mailbox_close(&mbox[8]);
+    }
+  } else if (warp == 0) {
     // ============================ TMA producer ============================
     if (lane == 0) {
       tma_prefetch_desc(&P.tmap_a[0]);
@@ -787,7 +1046,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       const int prof_empty = prof ? kProfProducerEmptyWait : -1;
       Work w;
       bool tail_taken = false;
-      for (int i = cta; next_work(i, tail_taken, pr == 0, w);) {
+      bool alive = true;  // false once a wait gave up: no further loads are issued
+      for (int i = cta; alive && next_work(i, tail_taken, pr == 0, w);) {
         const int k_lo = w.k_lo, k_hi = w.k_hi;
         const Tile t = walk.at(w.pos);
         if (!t.valid) continue;
@@ -813,8 +1073,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
                 const int id = s * P.ag_chunks + c;
                 if (id < 64 && ((seen_chunks >> id) & 1ull)) continue;  // acquired earlier
                 ProfTimer pa(prof);
-                wait_flag(P.flags[P.rank] + P.gather_flag_off + id, P.epoch,
-                          timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
+                alive = alive && wait_flag(P.flags[P.rank] + P.gather_flag_off + id, P.epoch,
+                                           timeout_ns, kTimeoutGatherFlag, (s << 16) | c);
                 pa.stop(kProfProducerFlagPoll);
                 if (id < 64) seen_chunks |= 1ull << id;
                 fresh = true;
@@ -829,14 +1089,17 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             pt.stop(kProfProducerGatherWait);
           }
         }
-        for (int seg = 0; seg < num_segs; ++seg) {
+        for (int seg = 0; alive && seg < num_segs; ++seg) {
           const int j0 = k_lo + seg * seg_kb, j1 = min(j0 + seg_kb, k_hi);
-          for (int pass = 0; pass < P.passes; ++pass) {
+          for (int pass = 0; alive && pass < P.passes; ++pass) {
             // split fp32: (lo,hi), (hi,lo), then (hi,hi) so the small terms meet a small accumulator
             const CUtensorMap* am = (P.passes == 3 && pass == 0) ? &P.tmap_a[1] : amap;
             const CUtensorMap* bm = (P.passes == 3 && pass == 1) ? &P.tmap_b[1] : &P.tmap_b[0];
             for (int j = j0; j < j1; ++j, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
-              wait_mbar(bar_empty + 8 * s, ph ^ 1u, timeout_ns, kTimeoutEmptyBar, it, prof_empty);
+              if (!wait_mbar(bar_empty + 8 * s, ph ^ 1u, timeout_ns, kTimeoutEmptyBar, it, prof_empty)) {
+                alive = false;
+                break;
+              }
               const uint32_t sa = smem_base + s * kStageBytes;
               if constexpr (kCG == 1) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
@@ -864,17 +1127,24 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       const int prof_full = prof ? kProfMmaFullWait : -1, prof_tmem = prof ? kProfMmaTmemWait : -1;
       Work w;
       bool tail_taken = false;
-      for (int i = cta; next_work(i, tail_taken, false, w);) {
+      bool alive = true;  // false once a wait gave up: no further MMAs are issued
+      for (int i = cta; alive && next_work(i, tail_taken, false, w);) {
         const int k_lo = w.k_lo, k_hi = w.k_hi;
         if (!walk.at(w.pos).valid) continue;
-        for (int seg = 0; seg < num_segs; ++seg, ++unit) {
+        for (int seg = 0; alive && seg < num_segs; ++seg, ++unit) {
           const uint32_t acc = unit & 1u;
-          wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit, prof_tmem);
+          if (!wait_mbar(bar_tempty + 8 * acc, ((unit >> 1) & 1u) ^ 1u, timeout_ns, kTimeoutTmemEmpty, unit, prof_tmem)) {
+            alive = false;
+            break;
+          }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kBN;
           const int nkb = (min(k_lo + (seg + 1) * seg_kb, k_hi) - (k_lo + seg * seg_kb)) * P.passes;
           for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0)) {
-            wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it, prof_full);
+            if (!wait_mbar(bar_full + 8 * s, ph, timeout_ns, kTimeoutFullBar, it, prof_full)) {
+              alive = false;
+              break;
+            }
             tc_fence_after();
             // stage s sits s * kStageBytes further on: only the address field (16-byte units) moves
             const uint64_t adesc = adesc0 + s * (kStageBytes >> 4);
@@ -888,6 +1158,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
             if constexpr (kCG == 1) umma_commit(bar_empty + 8 * s);
             else umma_commit_pair(bar_empty + 8 * s, 3);
           }
+          if (!alive) break;
           if constexpr (kCG == 1) umma_commit(bar_tfull + 8 * acc);
           else umma_commit_pair(bar_tfull + 8 * acc, 3);
         }
@@ -926,11 +1197,13 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     // scratch tile / flags of piece `idx` for this CTA's half of the tile
     auto tail_slot = [&](int idx) { return vr * lp.ctas_per_vrank + idx * kCG + static_cast<int>(pr); };
     // accumulator `u` -> fp32 tile at dst ([32-column chunk][row][32 floats]), optionally added to what is there
-    auto dump_accumulator = [&](uint32_t u, float* dst, bool add) {
+    // (returns false when the accumulator never became ready: the caller stops)
+    auto dump_accumulator = [&](uint32_t u, float* dst, bool add) -> bool {
       const uint32_t sacc = u & 1u;
+      uint32_t ready = 1u;
       if (lane == 0)
-        wait_mbar(bar_tfull + 8 * sacc, (u >> 1) & 1u, timeout_ns, kTimeoutTmemFull, u);
-      __syncwarp();
+        ready = wait_mbar(bar_tfull + 8 * sacc, (u >> 1) & 1u, timeout_ns, kTimeoutTmemFull, u) ? 1u : 0u;
+      if (!__shfl_sync(0xffffffffu, ready, 0)) return false;
       tc_fence_after();
       const uint32_t staddr = tmem_base + sacc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
@@ -956,6 +1229,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         if constexpr (kCG == 1) mbar_arrive(bar_tempty + 8 * sacc);
         else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * sacc, 0));
       }
+      return true;
     };
     // One of the `n_parts` pieces (K ranges) of a split tail tile.  The pieces run at the same time
     // on different CTAs and finish the tile together: piece p owns the 32-column chunks
@@ -993,14 +1267,16 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         char* blk = scratch + my_slot * kTileBytes + static_cast<size_t>(c * 4 + q) * kBlk + lane * 16;
 #pragma unroll
         for (int w = 0; w < 8; ++w)
-          st_global_v4(blk + w * 512, make_uint4(raw[4 * w], raw[4 * w + 1], raw[4 * w + 2], raw[4 * w + 3]));
+          if (EDM_ADDR_OK(blk + w * 512, 16, 13u))
+            st_global_v4(blk + w * 512, make_uint4(raw[4 * w], raw[4 * w + 1], raw[4 * w + 2], raw[4 * w + 3]));
       }
       pdump.stop(kProfEpiIssue);
       ProfTimer pfence(eprof);
       __threadfence();
       __syncwarp();
       pfence.stop(kProfEpiFence);
-      if (lane == 0) st_relaxed_sys(&g_tail_flags[my_slot * 4 + q], lp.tail_epoch);
+      if (lane == 0 && EDM_ADDR_OK(&g_tail_flags[my_slot * 4 + q], 4, 14u))
+        st_relaxed_sys(&g_tail_flags[my_slot * 4 + q], lp.tail_epoch);
       ProfTimer pwait(eprof);
       if (lane < n_parts && lane != part)
         wait_flag(&g_tail_flags[(slot0 + lane * kCG) * 4 + q], lp.tail_epoch, timeout_ns,
@@ -1017,8 +1293,11 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         uint32_t dst = land;
         for (int p = 0; p < n_parts; ++p) {
           if (p == part) continue;
-          for (int c = c_lo; c < c_hi; ++c, dst += kBlk)
-            bulk_load(dst, scratch + (slot0 + p * kCG) * kTileBytes + static_cast<size_t>(c * 4 + q) * kBlk, kBlk, my_bar);
+          for (int c = c_lo; c < c_hi; ++c, dst += kBlk) {
+            const char* from = scratch + (slot0 + p * kCG) * kTileBytes + static_cast<size_t>(c * 4 + q) * kBlk;
+            if (EDM_ADDR_OK(from, kBlk, 15u) && dst + kBlk <= smem_base + kPipeBytes) bulk_load(dst, from, kBlk, my_bar);
+            else mbar_complete_tx(my_bar, kBlk);
+          }
         }
       }
       wait_mbar(my_bar, 0u, timeout_ns, kTimeoutTailFlag, 0x100u | static_cast<uint32_t>(q));
@@ -1054,7 +1333,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
               o.z = __float_as_uint(v[w * 4 + 2]); o.w = __float_as_uint(v[w * 4 + 3]);
             }
             const int col = c * 32 + w * kOutPerVec;
-            if (n0 + col < P.N) st_global_v4(out_row + col * kOutBytes, o);
+            if (n0 + col < P.N && EDM_ADDR_OK(out_row + col * kOutBytes, 16, 16u)) st_global_v4(out_row + col * kOutBytes, o);
           }
         }
       }
@@ -1078,14 +1357,17 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       // this CTA's 128-row half of the tile: its slot / flag index at the owner
       const int slot_idx = t.owned_idx * kCG + static_cast<int>(pr);
       // every segment but the last is only folded into the running sum
-      for (int seg = 0; seg + 1 < num_segs; ++seg, ++unit) dump_accumulator(unit, my_scratch, seg > 0);
+      bool segs_ok = true;
+      for (int seg = 0; segs_ok && seg + 1 < num_segs; ++seg, ++unit) segs_ok = dump_accumulator(unit, my_scratch, seg > 0);
+      if (!segs_ok) break;
       const uint32_t tile_iter = unit++;
       const uint32_t acc = tile_iter & 1u;
+      uint32_t tile_ready = 1u;
       if (lane == 0) {
         ProfTimer pt(eprof);
-        wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter);
+        tile_ready = wait_mbar(bar_tfull + 8 * acc, (tile_iter >> 1) & 1u, timeout_ns, kTimeoutTmemFull, tile_iter) ? 1u : 0u;
         pt.stop(kProfEpiTmemWait);
-        if (settle_early && pend_new != nullptr) {
+        if (tile_ready && settle_early && pend_new != nullptr) {
           // Long tiles: the previous tile's copies were issued a whole tile time ago and have
           // landed by now, so its flag can go out one tile (not two) after the data.
           ProfTimer pw(eprof);
@@ -1095,7 +1377,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           pend_new = nullptr;
         }
       }
-      __syncwarp();
+      // (the shuffle also re-converges the warp) an accumulator that never became ready ends this
+      // warp's tile loop: nothing more is read from TMEM or shipped
+      if (!__shfl_sync(0xffffffffu, tile_ready, 0)) break;
       tc_fence_after();
       // Where the tile goes.  Fused modes: every tile -- this rank's own included -- is shipped
       // as a partial into the owner's window slot [source rank][slot]; the owner's reducer warps
@@ -1177,7 +1461,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           __syncwarp();
           if (lane == 0) {
             ProfTimer pi(eprof);
-            bulk_store(dst_base + (h * 4 + q) * kEpiWarpBytes, stage_smem, kEpiWarpBytes);
+            if (EDM_ADDR_OK(dst_base + (h * 4 + q) * kEpiWarpBytes, kEpiWarpBytes, 17u))
+              bulk_store(dst_base + (h * 4 + q) * kEpiWarpBytes, stage_smem, kEpiWarpBytes);
             bulk_commit();
             pi.stop(kProfEpiIssue);
           }
@@ -1193,7 +1478,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
           const int lv = lane & 15;
           const uint4 x = ld_shared_v4(stage_smem + lr * kEpiRowBytes + ((lv ^ (lr & 7)) << 4));
           const int col = col0 + lv * kOutPerVec;
-          if (q * 32 + lr < valid_rows && col < valid_cols)
+          if (q * 32 + lr < valid_rows && col < valid_cols &&
+              EDM_ADDR_OK(dst_base + static_cast<int64_t>(q * 32 + lr) * dst_ld + col * kOutBytes, 16, 18u))
             st_global_v4(dst_base + static_cast<int64_t>(q * 32 + lr) * dst_ld + col * kOutBytes, x);
         }
         __syncwarp();
@@ -1217,8 +1503,8 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
     if (eprof) atomicAdd(&g_prof[kProfEpiTileLoop], static_cast<unsigned long long>(globaltimer_ns() - epi_total.t0));
     if (lane == 0) {
       ProfTimer pfn(eprof);
+      bulk_wait_pending<0>();  // nothing of this warp's staging may be in flight when the CTA exits
       if (pend_new != nullptr) {
-        bulk_wait_pending<0>();
         if (pend_old != nullptr)
           mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_old)), timeout_ns);
         mailbox_post(&mbox[q], make_note(kNoteFlag, reinterpret_cast<uint64_t>(pend_new)), timeout_ns);
@@ -1248,52 +1534,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 
   else if (warp == 8) {
     // ============================ signaller ============================
-    // Lane w serves mailbox w.  A batch of notes costs one system-scope fence; the flag stores
-    // after it are relaxed (the fence already orders the landed data before them).
-    // (nothing is ever posted without an exchange: stay off the issue slots then)
-    if (lane < kMailboxes && P.world > 1 && P.mode != kPlain && !(P.mode == kAG && P.ag_external)) {
-      volatile Mailbox* mb = &mbox[lane];
-      uint32_t done = 0;
-      uint64_t idle_since = 0;
-      const int total_push_warps = (lp.ctas_per_vrank + max(lp.push_stride, 1) - 1) / max(lp.push_stride, 1) * kPushWarps;
-      while (true) {
-        const uint32_t ready = mb->ready;
-        if (ready != done) {
-          __threadfence_block();
-          fence_acq_rel_sys();
-          for (; done != ready; ++done) {
-            const uint64_t note = mb->note[done % kMailboxDepth];
-            const uint64_t kind = note >> 60, payload = note & ((1ull << 60) - 1);
-            if (kind == kNoteFlag) {
-              st_relaxed_sys(reinterpret_cast<uint32_t*>(payload), P.epoch);
-            } else if (kind == kNoteResult) {
-              for (int peer = 0; peer < P.world; ++peer)
-                if (peer != P.rank)
-                  st_relaxed_sys(P.flags[peer] + P.result_flag_off + static_cast<uint32_t>(payload), P.epoch);
-            } else {
-              const int peer = static_cast<int>(payload >> 24), c = static_cast<int>(payload & 0xFFFFFF);
-              uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
-              if (atomicAdd(ctr, 1u) == static_cast<uint32_t>(total_push_warps - 1)) {
-                // last push warp of this GPU: every piece of the chunk has been written
-                *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;
-                fence_acq_rel_sys();
-                st_relaxed_sys(P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c, P.epoch);
-              }
-            }
-          }
-          mb->done = done;
-          idle_since = 0;
-        } else if (mb->closed) {
-          if (mb->ready == done) break;
-        } else {
-          __nanosleep(1000);
-          if (aborted()) break;
-          const uint64_t now = globaltimer_ns();
-          if (idle_since == 0) idle_since = now;
-          else if (now - idle_since > 4 * timeout_ns) break;  // posters are bounded; this is a backstop
-        }
-      }
-    }
+    signaller_role();
   } else {
     // ============================ extra reducers / push warps (warps 9-11) ============================
     if (fused_reduce) reduce_units(&mbox[6 + (warp - 9)], false);
@@ -1310,7 +1551,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   if (aborted()) __nanosleep(200000);  // let loads that are still in flight land before smem goes away
   // a pair leaves together: the partner may still signal this CTA's barriers or read its smem
   if constexpr (kCG == 2) cluster_sync_all();
-  if (warp == 2) {
+  if (warp == 2 && !is_pusher) {
     tc_fence_after();
     tmem_dealloc<kCG>(tmem_base, kTmemCols);
   }

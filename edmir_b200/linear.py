@@ -27,8 +27,9 @@ def _check_2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must have unit stride along its last dimension")
 
 
-def _stream() -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _stream() -> int:
+    """Raw handle of torch's current stream on the current device (as an integer for ctypes)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def prepare_weight(w_kn: torch.Tensor) -> torch.Tensor:

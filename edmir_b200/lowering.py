@@ -7,16 +7,27 @@ reported in (``UOp``/``MovementDesc``/``EDMBuilder``, EDM-IR/ir/uop.py:44-142, b
 the analysis that scores candidates (analysis.py:36-65) and the way a measured run is turned
 into a graph (CUDA-event timing and ``edm.<ns>:<name>.iter<N>`` NVTX ranges,
 EDM-IR/ir/trace.py:26-43, :122-172, :204-266).
+
+A candidate is a ``schedule.Schedule``; its predicted execution is an EDM graph with integer
+nanosecond durations (``schedule_graph``): GEMM nodes per shard and chunk, transfer nodes per peer
+and chunk on the streams that carry them, flag publications, the launch itself.  The graph's
+critical path, evaluated by the native library with the reference's tie rules
+(``edm_graph_cost``), is the candidate's cost; the terms follow the reference's overlap model
+(paper/mlsys-2027/model.md:98 transfer = alpha + beta*m, :118 exposed = what the compute window
+does not cover, :161-168 what splitting and new contention cost).
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
+from functools import lru_cache
 from typing import Callable, Sequence
 
-from . import selector
-from .calibration import Calibration, cost_params, wire_bytes
+from . import _lib
+from .calibration import Calibration, gemm_ns, wire_bytes
 from .ir import EDMBuilder, EDMGraph, MovementDesc, TensorDesc
 from .ir import ops as irops
+from .schedule import Schedule
 
 OPS = ("gemm_rs", "gemm_ar", "ag_gemm")
 _COMM_OP = {"gemm_rs": irops.COMM_REDUCE_SCATTER, "gemm_ar": irops.COMM_ALL_REDUCE,
@@ -44,35 +55,226 @@ class TPLinearSpec:
             raise ValueError("M must be divisible by the number of ranks")
 
 
-@dataclass(frozen=True)
-class Schedule:
-    """A candidate: ``chunks == 1`` is the unfused sequence (GEMM kernel, then the collective);
-    ``chunks > 1`` is the fused kernel with that exchange granularity."""
-
-    index: int
-    chunks: int
-
-    @property
-    def fused(self) -> bool:
-        return self.chunks > 1
+# ---------------------------------------------------------------- candidates
+AG_PUSHER_CTAS = (4, 8, 16, 24, 32)
+AG_CHUNKS = (1, 2, 4, 8)
 
 
-def candidates(spec: TPLinearSpec, chunk_counts: Sequence[int] = selector.DEFAULT_CANDIDATES) -> list[Schedule]:
+def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedule]:
+    """The schedules a call can run with, indexed in the order returned.
+
+    Index 0 is the unfused sequence (this library's GEMM, then the ``torch.distributed``
+    collective): it is scored like the others so the model can say when fusion does not pay, but
+    ``select_schedule`` only picks it when asked to (it is a library collective, kept as the
+    comparison baseline).  All-gather + GEMM: kernel pushes by dedicated pusher CTAs (how many SMs
+    to give up) or by warps inside every GEMM CTA, copy engines on one or two side streams, or
+    both, each at several flag granularities.  GEMM + reduce-scatter / all-reduce have one fused
+    schedule: every tile is pushed as it is finished, there is no coarser granularity to choose."""
     if spec.world == 1:
-        return [Schedule(0, 1)]
-    out = []
-    for c in chunk_counts:
-        if spec.op == "ag_gemm" and c > spec.M // spec.world:
-            continue
-        out.append(Schedule(len(out), c))
-    return out
+        return [Schedule(index=0)]
+    out: list[Schedule] = []
+    if include_unfused:
+        out.append(Schedule(fused=False))
+    if spec.op != "ag_gemm":
+        out.append(Schedule())
+    else:
+        rows = spec.M // spec.world
+        chunk_ok = [c for c in AG_CHUNKS if c <= rows and (rows // c) >= 1]
+        for c in chunk_ok:
+            for p in AG_PUSHER_CTAS:
+                out.append(Schedule(chunks=c, transport="sm", pusher_ctas=p))
+        for c in chunk_ok[:3]:
+            out.append(Schedule(chunks=c, transport="sm", pusher_ctas=0))
+            for s in (1, 2):
+                out.append(Schedule(chunks=c, transport="ce", side_streams=s))
+        if spec.world > 2:
+            for c in chunk_ok[1:3]:
+                for p in (8, 16):
+                    for far in sorted({max(1, (spec.world - 1) // 3), (spec.world - 1) // 2}):
+                        out.append(Schedule(chunks=c, transport="hybrid", pusher_ctas=p, ce_peers=far, side_streams=1))
+    return [s.with_index(i) for i, s in enumerate(out)]
+
+
+# ---------------------------------------------------------------- predicted execution
+class _Plan:
+    """Tasks with integer durations and dependencies, laid out as soon as possible and emitted
+    through ``EDMBuilder`` in creation order (which is part of the tie-breaking contract)."""
+
+    def __init__(self, phase: str):
+        self.phase = phase
+        self.tasks: list[dict] = []
+
+    def add(self, kind: str, name: str, op: str, dur: int, deps: Sequence[int] = (), stream: str | None = None,
+            after: int | None = None, **kw) -> int:
+        """``after``: the previous task on the same stream (stream order); ``deps``: data dependencies."""
+        start = 0
+        for d in list(deps) + ([after] if after is not None else []):
+            start = max(start, self.tasks[d]["end"])
+        self.tasks.append({"kind": kind, "name": name, "op": op, "start": start, "end": start + max(int(dur), 0),
+                           "deps": list(deps), "after": after, "stream": stream, "kw": kw})
+        return len(self.tasks) - 1
+
+    def build(self, common: dict) -> EDMGraph:
+        b = EDMBuilder(default_phase=self.phase)
+        begin = b.phase_begin(self.phase, 0)
+        nodes = []
+        for t in self.tasks:
+            make = {"compute": b.compute, "comm": b.comm}.get(t["kind"])
+            if make is not None:
+                node = make(t["name"], t["start"], t["end"], op=t["op"], stream=t["stream"], **common, **t["kw"])
+            else:
+                node = b.uop(t["op"], t["name"], t["start"], t["end"], stream=t["stream"], **common, **t["kw"])
+            nodes.append(node)
+        end = b.phase_end(self.phase, max([t["end"] for t in self.tasks], default=0))
+        for i, t in enumerate(self.tasks):
+            if t["after"] is not None:
+                b.edge(nodes[t["after"]], nodes[i], irops.STREAM_ORDER)
+        for i, t in enumerate(self.tasks):
+            for d in t["deps"]:
+                b.data_edge(nodes[d], nodes[i], t["name"])
+        b.bind_phase(begin, end, *nodes)
+        return b.build()
+
+
+def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_rank: int | None = None) -> EDMGraph:
+    """The predicted execution of ``sched`` for ``spec`` as an EDM graph (durations in ns)."""
+    W = spec.world
+    wire = wire_bytes(spec.op, spec.M, spec.N, spec.K, W)
+    comm_op = _COMM_OP[spec.op]
+    group = tuple(range(W))
+    plan = _Plan("tp_linear")
+    attrs = {"schedule_index": sched.index, "schedule": sched.label()}
+    common = {"tp_rank": tp_rank}
+
+    def move(nbytes: int, backend: str) -> MovementDesc:
+        return MovementDesc(kind=comm_op.split(".", 1)[1], backend=backend, size_bytes=int(nbytes), group="tp",
+                            group_ranks=group)
+
+    if W == 1:
+        plan.add("compute", "gemm", irops.COMPUTE_GEMM, gemm_ns(spec.M, spec.N, spec.K, calib), stream="compute",
+                 attrs=dict(attrs))
+        return plan.build(common)
+
+    if not sched.fused:
+        # two launches: the library collective at its own rate, before (all-gather) or after the GEMM
+        coll = calib.launch_ns + int(wire / calib.nccl_gbs) + W * calib.skew_ns_per_rank
+        full = gemm_ns(spec.M, spec.N, spec.K, calib)
+        if spec.op == "ag_gemm":
+            m = plan.add("comm", "all_gather", comm_op, coll, stream="nccl", movement=move(wire, "nccl"), attrs=dict(attrs))
+            plan.add("compute", "gemm", irops.COMPUTE_GEMM, calib.launch_ns + full, deps=(m,), stream="compute",
+                     attrs=dict(attrs))
+        else:
+            g = plan.add("compute", "gemm", irops.COMPUTE_GEMM, calib.launch_ns + full, stream="compute", attrs=dict(attrs))
+            plan.add("comm", spec.op, comm_op, coll, deps=(g,), stream="nccl", movement=move(wire, "nccl"),
+                     attrs=dict(attrs))
+        return plan.build(common)
+
+    skew = (W - 1) * calib.skew_ns_per_rank
+    if spec.op == "ag_gemm":
+        c = sched.chunks
+        first_d = 1
+        ce_lo = {"sm": W, "ce": first_d, "hybrid": max(first_d, W - sched.ce_peers)}[sched.transport]
+        pushes = ce_lo > first_d
+        uses_ce = ce_lo < W
+        pushers = sched.pusher_ctas if pushes else 0
+        units = calib.gemm_units - pushers // 2
+        total = gemm_ns(spec.M, spec.N, spec.K, calib, units=units)
+        if pushes and pushers == 0:
+            total = int(total * calib.sm_push_slowdown)  # push warps share the GEMM CTAs' memory pipes
+        push_rate = min(calib.link_gbs, pushers * calib.pusher_cta_gbs) if pushers else calib.link_gbs
+        n_streams = min(max(sched.side_streams, 1), max(W - ce_lo, 1)) if uses_ce else 0
+        ce_rate = calib.ce_rate(n_streams) if uses_ce else 0.0
+        if pushes and uses_ce and push_rate + ce_rate > calib.link_gbs:  # both share the link
+            scale = calib.link_gbs / (push_rate + ce_rate)
+            push_rate, ce_rate = push_rate * scale, ce_rate * scale
+        shard = wire // (W - 1)
+        setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP,
+                         calib.launch_ns + skew + (calib.ce_launch_ns if uses_ce else 0), stream="compute")
+        # transfers: one chain per carrier, shards in the order their consumers need them
+        last = {"push": setup}
+        for s in range(n_streams):
+            last[f"ce{s}"] = setup
+        ready: dict = {}
+        for d in range(1, W):
+            if d < ce_lo:
+                stream, rate, backend = "push", push_rate, "nvlink-p2p"
+            else:
+                stream, rate, backend = f"ce{d % n_streams}", ce_rate / n_streams, "copy-engine"
+            for k in range(c):
+                nbytes = shard // c + (1 if k < shard % c else 0)
+                node = plan.add("comm", f"all_gather.s{d}.c{k}", comm_op, int(nbytes / rate), stream=stream,
+                                after=last[stream], movement=move(nbytes, backend),
+                                attrs={**attrs, "chunk": k, "shard": d})
+                last[stream] = node
+                # the chunk's flag becomes visible one publication later (not link time)
+                ready[(d, k)] = plan.add("other", f"flag.s{d}.c{k}", irops.EVENT_RECORD, calib.publish_ns,
+                                         deps=(node,), stream=stream + ".flags")
+        prev = setup
+        for j in range(W):
+            for k in range(c):
+                share = total // (W * c) + (1 if (j * c + k) < total % (W * c) else 0)
+                deps = (ready[(j, k)],) if j > 0 else ()
+                prev = plan.add("compute", f"gemm.s{j}.c{k}", irops.COMPUTE_GEMM, share, deps=deps, stream="compute",
+                                after=prev, attrs={**attrs, "chunk": k, "shard": j})
+        return plan.build(common)
+
+    # GEMM + reduce-scatter / all-reduce: tiles are pushed as they finish; modelled as G groups of
+    # tile rounds.  The last group's flags and its reduction at the owner cannot overlap anything.
+    tiles = -(-spec.M // 256) * -(-spec.N // 256)
+    rounds = max(1, -(-tiles // calib.gemm_units))
+    G = min(8, rounds)
+    total = gemm_ns(spec.M, spec.N, spec.K, calib)
+    push_bytes = wire if spec.op == "gemm_rs" else wire // 2
+    setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew, stream="compute")
+    g_prev, m_prev = setup, None
+    for i in range(G):
+        g_prev = plan.add("compute", f"gemm.{i}", irops.COMPUTE_GEMM, total // G + (1 if i < total % G else 0),
+                          stream="compute", after=g_prev, attrs={**attrs, "chunk": i})
+        nbytes = push_bytes // G + (1 if i < push_bytes % G else 0)
+        m_prev = plan.add("comm", f"{spec.op}.{i}", comm_op, int(nbytes / calib.link_gbs), deps=(g_prev,), stream="push",
+                          after=m_prev, movement=move(nbytes, "nvlink-p2p"), attrs={**attrs, "chunk": i})
+    flag = plan.add("other", "flags", irops.EVENT_RECORD, calib.publish_ns, deps=(m_prev,), stream="push.flags")
+    own_bytes = (spec.M // W if spec.op == "gemm_rs" else -(-spec.M // W)) * spec.N * 2
+    red = plan.add("compute", "reduce", irops.COMPUTE_OTHER, int(own_bytes * W / G / calib.reduce_gbs), deps=(flag,),
+                   stream="reduce", attrs=dict(attrs))
+    if spec.op == "gemm_ar":
+        # the owner stores the reduced tiles into every rank's output: the second half of the wire bytes
+        tail = wire // 2 // G
+        plan.add("comm", "gemm_ar.result", comm_op, int(tail / calib.link_gbs) + calib.publish_ns, deps=(red,),
+                 stream="push", movement=move(tail, "nvlink-p2p"), attrs=dict(attrs))
+    return plan.build(common)
+
+
+@dataclass(frozen=True)
+class ScheduleCost:
+    makespan: int       # critical-path duration, ns
+    exposed_comm: int   # duration of comm nodes on the critical path
+    total_comm: int
+
+
+def graph_cost(graph: EDMGraph) -> ScheduleCost:
+    """Critical path and exposed communication of a graph with integer durations, evaluated by
+    the native library (bit-exact with ``analyze_critical_path`` / ``analyze_exposure``)."""
+    ids = sorted(graph.uops)
+    pos = {u: i for i, u in enumerate(ids)}
+    n, m = len(ids), len(graph.edges)
+    dur = (C.c_int64 * max(n, 1))(*[int(graph.uops[u].end_us - graph.uops[u].start_us) for u in ids])
+    end = (C.c_int64 * max(n, 1))(*[int(graph.uops[u].end_us) for u in ids])
+    comm = (C.c_uint8 * max(n, 1))(*[1 if irops.is_comm(graph.uops[u].op) else 0 for u in ids])
+    src = (C.c_int32 * max(m, 1))(*[pos[e.src] for e in graph.edges])
+    dst = (C.c_int32 * max(m, 1))(*[pos[e.dst] for e in graph.edges])
+    makespan, exposed = C.c_int64(), C.c_int64()
+    _lib.check(_lib.load().edm_graph_cost(n, dur, end, comm, m, src, dst, C.byref(makespan), C.byref(exposed),
+                                          None, None), "edm_graph_cost")
+    total = sum(int(graph.uops[u].end_us - graph.uops[u].start_us) for u in ids if irops.is_comm(graph.uops[u].op))
+    return ScheduleCost(makespan.value, exposed.value, total)
 
 
 @dataclass(frozen=True)
 class Selection:
     spec: TPLinearSpec
     schedules: list
-    costs: list          # selector.CandidateCost per schedule
+    costs: list          # ScheduleCost per schedule
     chosen: int
     graphs: list         # candidate EDM graphs, same order
 
@@ -80,41 +282,46 @@ class Selection:
     def schedule(self) -> Schedule:
         return self.schedules[self.chosen]
 
+    @property
+    def predicted_us(self) -> float:
+        return self.costs[self.chosen].makespan / 1e3
 
-def select_schedule(spec: TPLinearSpec, calib: Calibration | None = None,
-                    chunk_counts: Sequence[int] = selector.DEFAULT_CANDIDATES, tp_rank: int | None = None) -> Selection:
-    """Score every candidate with the native cost model and return the arg-min (ties: lowest
-    index).  The unfused candidate is costed with the library collective's bandwidth, the fused
-    ones with the in-kernel push bandwidth; each is one ``edm_schedule_cost`` evaluation."""
-    calib = calib or Calibration.load()
-    scheds = candidates(spec, chunk_counts)
-    costs, graphs = [], []
-    for s in scheds:
-        p = cost_params(spec.op, spec.M, spec.N, spec.K, spec.world, calib, fused=s.fused)
-        costs.append(selector.schedule_cost(p, s.chunks))
-        graphs.append(selector.candidate_graph(p, s.chunks, spec.op if spec.world > 1 else "gemm_rs",
-                                               world=spec.world, tp_rank=tp_rank, schedule_index=s.index))
-    chosen = min(range(len(costs)), key=lambda i: (costs[i].makespan, i))
+
+@lru_cache(maxsize=256)
+def _select(spec: TPLinearSpec, calib: Calibration, allow_unfused: bool, tp_rank: int | None) -> Selection:
+    scheds = candidates(spec)
+    graphs = [schedule_graph(spec, s, calib, tp_rank) for s in scheds]
+    costs = [graph_cost(g) for g in graphs]
+    pool = [i for i, s in enumerate(scheds) if s.fused or allow_unfused or spec.world == 1]
+    chosen = min(pool, key=lambda i: (costs[i].makespan, i))
     return Selection(spec, scheds, costs, chosen, graphs)
+
+
+def select_schedule(spec: TPLinearSpec, calib: Calibration | None = None, allow_unfused: bool = False,
+                    tp_rank: int | None = None) -> Selection:
+    """Score every candidate and return the arg-min of the critical path (ties: lowest index).
+    The unfused sequence is scored too but only chosen with ``allow_unfused`` (it needs an
+    initialised ``torch.distributed`` group and is a library collective)."""
+    return _select(spec, calib or Calibration.load(), allow_unfused, tp_rank)
 
 
 # ---------------------------------------------------------------- launching
 def lower(spec: TPLinearSpec, ctx, schedule: Schedule) -> Callable:
     """Returns ``fn(a, b, out) -> out`` running ``schedule`` for ``spec``.
 
-    ``ctx`` is a ``symm.SymmetricContext`` (``None`` for a single rank).  The unfused schedule
-    uses this library's GEMM followed by the ``torch.distributed`` collective; fused schedules
-    are one launch of the fused kernel."""
+    ``ctx`` is a ``symm.SymmetricContext`` (``None`` for a single rank).  Fused schedules are one
+    launch of the fused kernel with every schedule field passed through ``edm_tp_call_t``; the
+    unfused schedule is this library's GEMM followed by the ``torch.distributed`` collective."""
     from . import linear
 
     if spec.world == 1 or ctx is None:
         return lambda a, b, out=None: linear.gemm(a, b, out)
     if schedule.fused:
         if spec.op == "ag_gemm":
-            return lambda x, w, out=None: ctx.ag_gemm(x, w, out, chunks=schedule.chunks)
+            return lambda x, w, out=None: ctx.ag_gemm(x, w, out, schedule=schedule)
         if spec.op == "gemm_rs":
-            return lambda a, b, out=None: ctx.gemm_rs(a, b, out)
-        return lambda a, b, out=None: ctx.gemm_ar(a, b, out)
+            return lambda a, b, out=None: ctx.gemm_rs(a, b, out, schedule=schedule)
+        return lambda a, b, out=None: ctx.gemm_ar(a, b, out, schedule=schedule)
 
     import torch
     import torch.distributed as dist
@@ -146,6 +353,14 @@ def nvtx_name(namespace: str, name: str, iteration: int | None = None) -> str:
     return base if iteration is None else f"{base}.iter{iteration}"
 
 
+def launch_range_name(spec: TPLinearSpec, iteration: int | None = None) -> str:
+    """NVTX range of one launch: it parses back to the op the launch's exchange stands for
+    (``comm.reduce_scatter`` ...), or ``compute.gemm`` on a single rank."""
+    if spec.world == 1:
+        return nvtx_name("compute", "gemm", iteration)
+    return nvtx_name("comm", _COMM_OP[spec.op].split(".", 1)[1], iteration)
+
+
 def measured_graph(spec: TPLinearSpec, schedule: Schedule, total_us: float, gemm_only_us: float,
                    tp_rank: int = 0, device: str | None = None, iteration: int | None = None) -> EDMGraph:
     """The observed execution of one call as an EDM graph: a ``compute.gemm`` node and a
@@ -159,7 +374,7 @@ def measured_graph(spec: TPLinearSpec, schedule: Schedule, total_us: float, gemm
     begin = b.phase_begin("tp_linear", 0.0)
     common = dict(tp_rank=tp_rank, device=device,
                   attrs={"schedule_index": schedule.index, "chunks": schedule.chunks, "fused": schedule.fused,
-                         "M": spec.M, "N": spec.N, "K": spec.K})
+                         "schedule": schedule.label(), "M": spec.M, "N": spec.N, "K": spec.K})
     gemm = b.compute("gemm" if iteration is None else f"gemm.iter{iteration}", 0.0, gemm_only_us,
                      op=irops.COMPUTE_GEMM, stream="compute",
                      tensor=TensorDesc(name="out", shape=(spec.M, spec.N), dtype=spec.dtype), **common)
@@ -194,8 +409,7 @@ def run_measured(spec: TPLinearSpec, ctx, schedule: Schedule, a, b, out=None, it
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(iters):
-        torch.cuda.nvtx.range_push(nvtx_name("compute" if not schedule.fused else "comm",
-                                             f"tp_linear.{spec.op}", i))
+        torch.cuda.nvtx.range_push(launch_range_name(spec, i))
         out = fn(a, b, out)
         torch.cuda.nvtx.range_pop()
     e1.record()

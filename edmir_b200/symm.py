@@ -19,9 +19,11 @@ import torch
 
 from . import _lib
 from .linear import _check_2d, _require_cuda, _stream
+from .schedule import Schedule
 
 _OPS = {"gemm_rs": _lib.EDM_OP_GEMM_RS, "gemm_ar": _lib.EDM_OP_GEMM_AR, "ag_gemm": _lib.EDM_OP_AG_GEMM}
-_TRANSPORTS = {"sm": _lib.EDM_TRANSPORT_SM, "ce": _lib.EDM_TRANSPORT_COPY_ENGINE}
+_TRANSPORTS = {"sm": _lib.EDM_TRANSPORT_SM, "ce": _lib.EDM_TRANSPORT_COPY_ENGINE,
+               "hybrid": _lib.EDM_TRANSPORT_HYBRID}
 _DTYPES = {torch.bfloat16: _lib.EDM_DTYPE_BF16, torch.float32: _lib.EDM_DTYPE_FP32}
 
 
@@ -56,6 +58,8 @@ class SymmetricContext:
                        "edm_comm_create")
         self._h = handle
         self._workspace: torch.Tensor | None = None
+        self._calls: dict = {}
+        self._tp_launch = self._lib.edm_tp_launch  # bound once: attribute lookups on a CDLL are slow
 
     # ---------------------------------------------------------------- setup
     @classmethod
@@ -99,12 +103,26 @@ class SymmetricContext:
     def reset_heap(self) -> None:
         _lib.check(self._lib.edm_comm_heap_reset(self._h), "edm_comm_heap_reset")
 
+    def poison(self, byte_value: int = 0xFF) -> None:
+        """Fill this rank's window (tile slots / gather buffers, both halves) with ``byte_value``
+        on the current stream; 0xFF makes every element a NaN, so a read of data that has not
+        arrived yet becomes visible in the result.  Call it only between launches."""
+        _lib.check(self._lib.edm_comm_poison(self._h, byte_value, _stream()), "edm_comm_poison")
+
     def p2p_probe(self, peer: int, nbytes: int, mode: int = 0) -> None:
         """Launch one link-probe copy of ``nbytes`` into ``peer``'s window (time it with events)."""
         _lib.check(self._lib.edm_comm_p2p_probe(self._h, peer, nbytes, mode, _stream()), "edm_comm_p2p_probe")
 
     # ---------------------------------------------------------------- launches
-    def _call(self, op: str, a, b, out, chunks: int = 1, transport: str = "sm") -> "_lib.TpCall":
+    def _call(self, op: str, a, b, out, schedule: Schedule | None = None) -> "_lib.TpCall":
+        """Validated ``edm_tp_call_t`` for one launch.  Built once per distinct (operands, schedule)
+        and kept: a steady-state launch is a dictionary lookup plus the library call."""
+        sched = schedule or Schedule()
+        key = (op, a.data_ptr(), b.data_ptr(), out.data_ptr(), a.shape, b.shape, out.shape, a.stride(0),
+               b.stride(0), out.stride(0), a.dtype, sched)
+        call = self._calls.get(key)
+        if call is not None:
+            return call
         _require_cuda(a, b, out)
         for t, n in ((a, "a"), (b, "b"), (out, "out")):
             _check_2d(t, n)
@@ -117,50 +135,69 @@ class SymmetricContext:
         want = (M // self.world, N) if op == "gemm_rs" else (M, N)
         if tuple(out.shape) != want:
             raise ValueError(f"out must have shape {want} for {op}, got {tuple(out.shape)}")
+        if not sched.fused:
+            raise ValueError("an unfused schedule is not a launch of the fused kernel")
         call = _lib.TpCall()
         call.op, call.dtype = _OPS[op], _DTYPES[a.dtype]
         call.a, call.lda = a.data_ptr(), a.stride(0)
         call.b, call.ldb = b.data_ptr(), b.stride(0)
         call.d, call.ldd = out.data_ptr(), out.stride(0)
         call.M, call.N, call.K = M, N, K
-        call.chunks = chunks
-        if transport not in _TRANSPORTS:
-            raise ValueError(f"transport must be one of {sorted(_TRANSPORTS)}")
-        call.transport = _TRANSPORTS[transport]
+        call.chunks = sched.chunks
+        call.transport = _TRANSPORTS[sched.transport]
+        call.pusher_ctas, call.ce_peers, call.side_streams = sched.pusher_ctas, sched.ce_peers, sched.side_streams
+        call.band_rows, call.band_cols = sched.band_rows, sched.band_cols
         if a.dtype == torch.float32:
             need = int(self._lib.edm_gemm_fp32_workspace_bytes(a.shape[0], N, K))
             if self._workspace is None or self._workspace.numel() < need:
                 self._workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+                self._calls.clear()  # cached calls point at the old workspace
             call.workspace, call.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
+        if len(self._calls) >= 256:
+            self._calls.clear()
+        self._calls[key] = call
         return call
 
-    def _launch(self, op: str, a, b, out, chunks: int = 1, transport: str = "sm"):
-        call = self._call(op, a, b, out, chunks, transport)
-        _lib.check(self._lib.edm_tp_launch(self._h, C.byref(call), _stream()), f"edm_tp_launch({op})")
+    def _launch(self, op: str, a, b, out, schedule: Schedule | None = None):
+        call = self._call(op, a, b, out, schedule)
+        rc = self._tp_launch(self._h, C.byref(call), _stream())
+        if rc:
+            _lib.check(rc, f"edm_tp_launch({op})")
         return out
 
-    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
+                schedule: Schedule | None = None) -> torch.Tensor:
         """Row-parallel linear + reduce-scatter: ``out[M/W, N]`` = rows ``rank*M/W ..`` of
         ``sum_r a_r @ b_r^T``."""
         if out is None:
             out = torch.empty((a.shape[0] // self.world, b.shape[0]), dtype=a.dtype, device=a.device)
-        return self._launch("gemm_rs", a, b, out)
+        return self._launch("gemm_rs", a, b, out, schedule)
 
-    def gemm_ar(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def gemm_ar(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
+                schedule: Schedule | None = None) -> torch.Tensor:
         """Row-parallel linear + all-reduce: every rank ends with ``sum_r a_r @ b_r^T``.  ``out``
         must come from ``self.empty`` (peers store reduced tiles straight into it)."""
         if out is None:
             out = self.empty((a.shape[0], b.shape[0]), a.dtype)
-        return self._launch("gemm_ar", a, b, out)
+        return self._launch("gemm_ar", a, b, out, schedule)
 
     def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-                chunks: int = 1, transport: str = "ce") -> torch.Tensor:
+                chunks: int | None = None, transport: str | None = None,
+                schedule: Schedule | None = None) -> torch.Tensor:
         """All-gather of the token-sharded ``x[M/W, K]`` fused with ``out[M, N/W] = X @ w^T``.
-        ``transport="sm"``: warps of the GEMM kernel push the shard; ``"ce"``: copy engines on the
-        library's side stream deliver it and the kernel only waits for the chunk flags."""
+
+        ``schedule`` says how the shards travel (see ``schedule.Schedule``): pushed by the kernel
+        -- by warps inside every GEMM CTA, or by ``pusher_ctas`` CTAs that do nothing else --,
+        delivered by copy engines on the library's side streams, or both.  ``chunks`` and
+        ``transport`` alone are shorthand for ``Schedule(chunks=..., transport=...)``; the default
+        is copy engines, one chunk."""
+        if schedule is None:
+            schedule = Schedule(chunks=chunks or 1, transport=transport or "ce")
+        elif chunks is not None or transport is not None:
+            raise ValueError("pass either a schedule or chunks/transport, not both")
         if out is None:
             out = torch.empty((x.shape[0] * self.world, w.shape[0]), dtype=x.dtype, device=x.device)
-        return self._launch("ag_gemm", x, w, out, chunks, transport)
+        return self._launch("ag_gemm", x, w, out, schedule)
 
 
 class EmulatedGroup:
@@ -177,15 +214,22 @@ class EmulatedGroup:
                 if a is not b:
                     _lib.check(lib.edm_comm_link_local(a._h, b.rank, b._h), "edm_comm_link_local")
 
-    def run(self, op: str, a_list, b_list, out_list, chunks: int = 1, transport: str = "sm"):
+    def run(self, op: str, a_list, b_list, out_list, chunks: int | None = None, transport: str | None = None,
+            schedule: Schedule | None = None):
+        if schedule is None:
+            schedule = Schedule(chunks=chunks or 1, transport=transport or "sm")
         calls = (_lib.TpCall * self.world)()
         for r, ctx in enumerate(self.ranks):
-            calls[r] = ctx._call(op, a_list[r], b_list[r], out_list[r], chunks, transport)
+            calls[r] = ctx._call(op, a_list[r], b_list[r], out_list[r], schedule)
         handles = (C.c_void_p * self.world)(*[ctx._h for ctx in self.ranks])
         lib = self.ranks[0]._lib
         _lib.check(lib.edm_tp_launch_emulated(handles, calls, self.world, _stream()),
                    f"edm_tp_launch_emulated({op})")
         return out_list
+
+    def poison(self, byte_value: int = 0xFF) -> None:
+        for ctx in self.ranks:
+            ctx.poison(byte_value)
 
     def close(self) -> None:
         for ctx in self.ranks:
@@ -193,17 +237,17 @@ class EmulatedGroup:
 
 
 def tile_walk(op: str, rank: int, world: int, M: int, N: int, tile_m: int = 256, tile_n: int = 256,
-              band_rows: int = 0, units: int = 74) -> list[tuple[int, int, int, int]]:
+              band_rows: int = 0, units: int = 74, band_cols: int = 0) -> list[tuple[int, int, int, int]]:
     """Order in which rank ``rank`` computes the output tiles of an ``[M, N]`` launch, as
     ``(row_block, col_block, owner, index_among_owner's_tiles)``; holes of the all-reduce walk
     have row and column -1.  Evaluated on the host by the same code the kernel runs."""
     lib = _lib.load()
     code = _lib.EDM_OP_GEMM if op == "gemm" else _OPS[op]
     n = C.c_int64()
-    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, units, None, 0, C.byref(n)),
+    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, band_cols, units, None, 0, C.byref(n)),
                "edm_tile_walk")
     buf = (C.c_int32 * (4 * n.value))()
-    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, units, buf, n.value,
+    _lib.check(lib.edm_tile_walk(code, rank, world, M, N, tile_m, tile_n, band_rows, band_cols, units, buf, n.value,
                                  C.byref(n)), "edm_tile_walk")
     return [tuple(buf[4 * i:4 * i + 4]) for i in range(n.value)]
 

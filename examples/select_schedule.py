@@ -25,18 +25,17 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=3584)
     ap.add_argument("--tp", type=int, default=8)
-    ap.add_argument("--candidates", default="1,2,4,8")
+    ap.add_argument("--allow-unfused", action="store_true", help="let the library collective win if it scores best")
     ap.add_argument("--show-graphs", action="store_true")
     ap.add_argument("--save-graph", metavar="PATH", help="write the chosen candidate's EDM graph as JSON")
     args = ap.parse_args()
 
     spec = lowering.TPLinearSpec(args.op, args.tokens, args.n, args.k, args.tp)
-    sel = lowering.select_schedule(spec, Calibration.load(), [int(c) for c in args.candidates.split(",")])
+    sel = lowering.select_schedule(spec, Calibration.load(), allow_unfused=args.allow_unfused)
     print(f"{spec}")
     for s, c in zip(sel.schedules, sel.costs):
         mark = "*" if s.index == sel.chosen else " "
-        kind = "fused" if s.fused else "unfused"
-        print(f"{mark} [{s.index}] chunks={s.chunks:<3d} {kind:8s} makespan={c.makespan / 1e3:9.1f} us "
+        print(f"{mark} [{s.index:2d}] {s.label():22s} makespan={c.makespan / 1e3:9.1f} us "
               f"exposed_comm={c.exposed_comm / 1e3:8.1f} us total_comm={c.total_comm / 1e3:8.1f} us")
     if args.show_graphs:
         g = sel.graphs[sel.chosen]

@@ -7,8 +7,9 @@ prints what the cost model predicted next to what was measured.
 
 Default shape: the Llama-3-8B-shaped row-parallel down_proj (weights [14336/TP, 4096], GEMM +
 all-reduce).  ``--op ag_gemm`` / ``gemm_rs`` run the other layer ops; for ``ag_gemm`` ``--k-total``
-is K and ``--n`` is divided by TP.  Candidate 0 (1 chunk) is the unfused sequence (this library's
-GEMM, then the torch.distributed collective); the others are the fused kernel.
+is K and ``--n`` is divided by TP.  Candidate 0 is the unfused sequence (this library's GEMM,
+then the torch.distributed collective); the others are schedules of the fused kernel
+(``--max-candidates`` best-scoring ones are run).
 """
 from __future__ import annotations
 
@@ -32,6 +33,7 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--tokens", default="1,16,128,1024,8192")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--max-candidates", type=int, default=8)
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
@@ -61,7 +63,9 @@ def main() -> None:
         sel = lowering.select_schedule(spec, calib, tp_rank=rank)
         out = ctx.empty((M, N), torch.bfloat16) if (ctx is not None and args.op == "gemm_ar") else None
         measured = []
-        for sched in sel.schedules:
+        ranked = sorted(range(len(sel.schedules)), key=lambda i: (sel.costs[i].makespan, i))
+        run = sorted(set(ranked[:args.max_candidates]) | {0, sel.chosen})
+        for sched in [sel.schedules[i] for i in run]:
             fn = lowering.lower(spec, ctx, sched)
             for _ in range(3):
                 fn(a, b, out)
@@ -80,10 +84,9 @@ def main() -> None:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             measured.append(float(t.item()))
         if rank == 0:
-            best = min(range(len(measured)), key=lambda i: measured[i])
-            cells = "  ".join(f"[{s.index}] c={s.chunks} {'fused' if s.fused else 'unfused'} "
-                              f"model {c.makespan / 1e3:.1f} measured {m:.1f}"
-                              for s, c, m in zip(sel.schedules, sel.costs, measured))
+            best = run[min(range(len(measured)), key=lambda i: measured[i])]
+            cells = "  ".join(f"[{i}] {sel.schedules[i].label()} model {sel.costs[i].makespan / 1e3:.1f} measured {m:.1f}"
+                              for i, m in zip(run, measured))
             print(f"{args.op} tp{world} M={M} N={N} K={K}: chosen [{sel.chosen}], fastest [{best}] | {cells}", flush=True)
     st = linear.status()
     assert st[0] == 0, st[:8]

@@ -45,6 +45,9 @@ extern "C" {
  * engines do not compete with the GEMM for the SMs' memory pipelines. */
 #define EDM_TRANSPORT_SM 0
 #define EDM_TRANSPORT_COPY_ENGINE 1
+/* HYBRID: the `ce_peers` farthest peers (rank-d for the largest d; their consumers need the shard
+ * last) are served by copy engines, the nearer ones by the kernel. */
+#define EDM_TRANSPORT_HYBRID 2
 
 #define EDM_MAX_RANKS 8
 #define EDM_IPC_HANDLE_BYTES 64
@@ -60,6 +63,11 @@ int edm_last_cuda_error(void);
  * mma.cu:119-136; here errors are returned, never fatal.) */
 int edm_status_read(uint32_t out[16]);
 int edm_status_clear(void);
+/* Synchronises the device and returns EDM_ERR_DEVICE_TIMEOUT if a bounded wait has expired since
+ * the last edm_status_clear(), EDM_OK otherwise.  The launch entry points themselves are
+ * asynchronous and cannot report it: after an expiry every later wait of every later launch falls
+ * through (so nothing ever hangs), which leaves outputs undefined until edm_status_clear(). */
+int edm_status_check(void);
 
 /* Device-side accounting for tracing (the reference times phases with CUDA events only,
  * EDM-IR/ir/trace.py:38-43; this looks inside a launch).  While enabled, every launch adds the
@@ -129,6 +137,12 @@ int edm_comm_link_local(edm_comm_t* comm, int peer, edm_comm_t* peer_comm);
 /* Bump allocation from the symmetric heap; every rank must make the same sequence of calls. */
 int edm_comm_heap_alloc(edm_comm_t* comm, size_t bytes, void** out);
 int edm_comm_heap_reset(edm_comm_t* comm);
+/* Debugging aid (no reference counterpart): fills this rank's window (both halves: tile slots and
+ * gather buffers, not the flag words) with `byte_value`, asynchronously on `stream`.  With 0xFF
+ * every bf16 / fp32 element there is a NaN, so a launch that reads a slot or a gathered row before
+ * its sender wrote it shows up in the output instead of silently re-using the previous call's
+ * data.  Every rank must have finished its previous launch (no copies in flight). */
+int edm_comm_poison(edm_comm_t* comm, int byte_value, void* stream);
 /* Link probe for calibration: copies `bytes` (a multiple of 8192, at most half the window) from
  * this rank's window into `peer`'s with mode 0 = 16-byte stores from every thread, mode 1 =
  * 8 KiB bulk copies staged through shared memory.  The caller times it with CUDA events; the
@@ -137,15 +151,15 @@ int edm_comm_heap_reset(edm_comm_t* comm);
 int edm_comm_p2p_probe(edm_comm_t* comm, int peer, size_t bytes, int mode, void* stream);
 /* The order in which one rank's CTAs take the output tiles of a launch (host-side evaluation of
  * the enumeration the kernel uses; no device work).  tile_m is 128, or 256 when a CTA pair shares
- * a tile; tile_n 256 (32 for decode-sized plain GEMMs); band_rows 0 = default; units = CTAs (or
- * pairs) of the launch.  Writes *positions = length of the walk and, when `out` is not NULL and
+ * a tile; tile_n 256 (32 for decode-sized plain GEMMs); band_rows 0 = default; band_cols = column
+ * blocks per super-tile of a band (0 = the whole width); units = CTAs (or pairs) of the launch.  Writes *positions = length of the walk and, when `out` is not NULL and
  * holds `capacity` >= *positions entries, four int32 per position: row block, column block (both
  * -1 for a hole of the all-reduce walk), owner rank, index among the owner's tiles.  No
  * reference counterpart (the reference has no multi-tile launch, ir/c-extension/mma.cu:168-176);
  * used by the CPU tests to check that every tile is produced exactly once per rank and that all
  * ranks agree on owners and slots. */
 int edm_tile_walk(int op, int rank, int world, int64_t M, int64_t N, int tile_m, int tile_n, int band_rows,
-                  int units, int32_t* out, int64_t capacity, int64_t* positions);
+                  int band_cols, int units, int32_t* out, int64_t capacity, int64_t* positions);
 /* How a launch of `tiles` output tiles on `units` CTAs (or CTA pairs) with `k_blocks` blocks of 128
  * bytes along K treats an incomplete last wave (host-side evaluation, no device work):
  * out[0] = tiles computed whole, out[1] = tiles of the last wave that are split along K,
@@ -182,6 +196,15 @@ typedef struct {
   int32_t transport; /* AG_GEMM: EDM_TRANSPORT_*; ignored otherwise */
   void* workspace; /* EDM_DTYPE_FP32 only: tf32 split scratch */
   size_t workspace_bytes;
+  /* Schedule fields (what the selector chooses besides `chunks` and `transport`); 0 = default. */
+  int32_t pusher_ctas;  /* AG_GEMM, kernel-side pushes: this many CTAs (rounded down to whole CTA pairs)
+                           take no tiles and only move the shard, with bulk copies staged through
+                           their shared memory; 0 = warps inside every GEMM CTA push with 16-byte stores */
+  int32_t ce_peers;     /* AG_GEMM, EDM_TRANSPORT_HYBRID: peers served by copy engines (0 .. world-1) */
+  int32_t side_streams; /* AG_GEMM, copy engines: streams the copies are spread over (1 .. 4; 0 = 2) */
+  int32_t band_rows;    /* tile walk: row blocks per band (0 = default) */
+  int32_t band_cols;    /* tile walk: column blocks per super-tile of a band (0 = the whole width) */
+  int32_t reserved;
 } edm_tp_call_t;
 
 /* Not capturable: the flags of the exchange carry the context's call counter, which a graph replay
@@ -233,6 +256,19 @@ int edm_schedule_cost(const edm_cost_params_t* p, int32_t chunks, edm_candidate_
  * *chosen; costs may be NULL. */
 int edm_select_schedule(const edm_cost_params_t* p, const int32_t* candidates, int32_t n,
                         edm_candidate_cost_t* costs, int32_t* chosen);
+
+/* The same evaluation for an arbitrary graph (the candidates of the all-gather and reduce-scatter
+ * schedules have one GEMM node per shard or tile round, pushes per peer, a final reduction; they
+ * are built with the EDMBuilder API and scored here).  Nodes are 0 .. n_nodes-1 in id order with
+ * integer durations, the end timestamps that take part in tie-breaking, and a flag for comm.*
+ * nodes; edges are (src, dst) in insertion order.  Returns the critical-path duration, the summed
+ * duration of comm nodes on it and, when `path` is not NULL, the node ids of the path
+ * (*path_len: capacity in, length out).  A cycle or an edge to an unknown node is EDM_ERR_BAD_ARG.
+ * Bit-exact with analyze_critical_path / analyze_exposure (EDM-IR/ir/analysis.py:36-65, :89-123)
+ * for integer durations. */
+int edm_graph_cost(int32_t n_nodes, const int64_t* dur, const int64_t* end, const uint8_t* is_comm,
+                   int32_t n_edges, const int32_t* src, const int32_t* dst, int64_t* makespan,
+                   int64_t* exposed_comm, int32_t* path, int32_t* path_len);
 
 #ifdef __cplusplus
 }

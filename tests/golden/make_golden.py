@@ -9,7 +9,12 @@ Imports the reference's own ``ir`` package from the directory given on the comma
 * ``selector_golden.json`` -- chunked GEMM->collective pipeline candidates built with the
   reference's ``EDMBuilder`` and scored with its ``analyze_critical_path`` /
   ``analyze_exposure``, for a sweep of integer cost parameters and chunk counts;
-* ``gain_golden.json`` -- ``classify_gain`` labels around its thresholds.
+* ``gain_golden.json`` -- ``classify_gain`` labels around its thresholds;
+* ``trace_golden.json`` -- the six-node graphs the reference's overlap probe builds from three
+  measured intervals (ir/trace.py:204-266), with their analysis results and text dumps;
+* ``nsys_golden.json`` -- a small hand-made profile (the rows of an Nsight Systems sqlite export:
+  NVTX ranges named by the ``edm.<ns>:<name>.iter<N>`` grammar, runtime calls, kernels, memcpys)
+  and what the reference's exporter (ir/nsys_export.py:211-314) makes of it.
 The reference is only needed to regenerate; tests read the JSON.
 """
 from __future__ import annotations
@@ -144,7 +149,86 @@ def selector_cases() -> list:
     return cases
 
 
+def trace_cases() -> list:
+    from ir import trace as ref_trace
+    from ir.printing import format_uops
+
+    cases = []
+    for kw in (dict(copy_us=100.0, compute_us=250.5, bytes_moved=8 << 20, device="cuda:0/sm_100", matrix=2048,
+                    dtype="bfloat16", wait_us=3.25, iteration=0),
+               dict(copy_us=700.125, compute_us=90.0, bytes_moved=1 << 25, device="cuda:0", matrix=4096,
+                    dtype="float32", wait_us=0.0, iteration=7)):
+        g = ref_trace.build_graph(**kw)
+        d = dump_graph(g)
+        d["args"] = kw
+        d["text"] = format_uops(g)
+        d["edge_attrs"] = [dict(e.attrs) for e in g.edges]
+        cases.append(d)
+    return cases
+
+
+NSYS_PROFILE = {
+    # table -> (columns, rows); times in ns
+    "StringIds": (("id", "value"), [[1, "cudaLaunchKernelExC_v11060"], [2, "cudaMemcpyAsync_v3020"],
+                                    [3, "void edm::tp_gemm_kernel<2, 256, false, __nv_bfloat16>(edm::LaunchParams)"],
+                                    [4, "void edm::split_tf32_kernel(float const*, float*, float*, long, long, long)"]]),
+    "NVTX_EVENTS": (("start", "end", "text", "globalTid"), [
+        [1000, 90000, "edm.phase:trace.iter0", 77],
+        [2000, 20000, "edm.kv:transfer.h2d.iter0", 77],
+        [21000, 23000, "edm.event:wait.copy_done.iter0", 77],
+        [24000, 60000, "edm.compute:qkv.matmul.iter0", 77],
+        [100000, 180000, "edm.comm:reduce_scatter.iter1", 77],
+        [181000, 260000, "edm.comm:all_gather.iter1", 77],
+        [300000, 310000, "edm.compute:gemm", 78],
+        [320000, 330000, "not an edm range", 78],
+        [340000, None, "edm.compute:gemm.iter9", 78],
+    ]),
+    "CUPTI_ACTIVITY_KIND_RUNTIME": (("start", "end", "correlationId", "nameId", "globalTid"), [
+        [3000, 4000, 11, 2, 77], [25000, 26000, 12, 1, 77], [27000, 28000, 13, 1, 77],
+        [101000, 102000, 14, 1, 77], [182000, 183000, 15, 1, 77], [184000, 185000, 16, 2, 77],
+        [301000, 302000, 17, 1, 78], [500000, 501000, 18, 1, 78],
+    ]),
+    "CUPTI_ACTIVITY_KIND_KERNEL": (("start", "end", "streamId", "correlationId", "demangledName"), [
+        [30000, 31000, 7, 12, 4], [31500, 58000, 7, 13, 3], [103000, 175000, 7, 14, 3],
+        [186000, 255000, 7, 15, 3], [303000, 309000, 7, 17, 3], [502000, 503000, 7, 18, 3],
+    ]),
+    "CUPTI_ACTIVITY_KIND_MEMCPY": (("start", "end", "streamId", "correlationId", "bytes", "copyKind"), [
+        [5000, 19000, 13, 11, 8388608, 1], [186500, 240000, 14, 16, 16777216, 8],
+    ]),
+    "ENUM_CUDA_MEMCPY_OPER": (("id", "label"), [[1, "CUDA_MEMCPY_KIND_HTOD"], [8, "CUDA_MEMCPY_KIND_DTOD"]]),
+}
+
+
+def nsys_case() -> dict:
+    import csv
+    import sqlite3
+    import tempfile
+
+    from ir.nsys_export import export_nsys, parse_edm_text
+
+    with tempfile.TemporaryDirectory() as tmp:
+        db = os.path.join(tmp, "profile.sqlite")
+        with sqlite3.connect(db) as conn:
+            for table, (cols, rows) in NSYS_PROFILE.items():
+                conn.execute(f'create table "{table}" ({", ".join(cols)})')
+                conn.executemany(f'insert into "{table}" values ({", ".join("?" for _ in cols)})', rows)
+        out = os.path.join(tmp, "out")
+        export_nsys(db, out)
+        tables = {}
+        for name in ("edm_nvtx_ranges", "edm_cuda_events", "edm_iteration_summary"):
+            with open(os.path.join(out, name + ".csv"), newline="") as f:
+                tables[name] = list(csv.DictReader(f))
+    texts = ["edm.compute:qkv.matmul.iter3", "edm.comm:reduce_scatter", "edm.phase:trace.iter12", "edm.odd",
+             "plain text.iter4", "edm.kv:transfer.h2d.iter0", "edm.comm:tp_linear.ag_gemm.iter10", "edm.a:b:c.iter1"]
+    return {"profile": {t: {"columns": list(c), "rows": r} for t, (c, r) in NSYS_PROFILE.items()},
+            "export": tables, "grammar": [[t, list(parse_edm_text(t))] for t in texts]}
+
+
 def main() -> None:
+    with open(os.path.join(HERE, "trace_golden.json"), "w") as f:
+        json.dump(trace_cases(), f, indent=1)
+    with open(os.path.join(HERE, "nsys_golden.json"), "w") as f:
+        json.dump(nsys_case(), f, indent=1)
     with open(os.path.join(HERE, "analysis_golden.json"), "w") as f:
         json.dump(reference_test_graphs(), f, indent=1)
     cases = selector_cases()

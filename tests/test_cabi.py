@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported_and_bound(native_lib):
 
 
 def test_struct_layouts_match_header():
-    assert C.sizeof(_lib.TpCall) == 104
+    assert C.sizeof(_lib.TpCall) == 128
     assert C.sizeof(_lib.CostParams) == 56
     assert C.sizeof(_lib.CandidateCost) == 40
 
@@ -39,6 +39,12 @@ def test_argument_validation_without_device(native_lib):
     assert native_lib.edm_gemm_bf16(16, 8, 16, 8, 16, 8, 0, 8, 8, None) == _lib.EDM_ERR_BAD_ARG
     assert native_lib.edm_gemm_fp32_workspace_bytes(0, 1, 1) == 0
     assert native_lib.edm_gemm_fp32_workspace_bytes(256, 1024, 512) == 2 * 4 * (256 * 512 + 1024 * 512) + 256 * 128 * 256 * 4
+    # extents whose byte counts would wrap around size_t are refused, not truncated
+    assert native_lib.edm_gemm_fp32_workspace_bytes(1 << 30, 1 << 30, 1 << 30) == 0
+    assert native_lib.edm_gemm_fp32_static(16, 1 << 30, 16, 1 << 30, 16, 1 << 30, 1 << 30, 1 << 30, 1 << 30,
+                                           None) == _lib.EDM_ERR_CAPACITY
+    assert native_lib.edm_gemm_fp32(16, 1 << 30, 16, 1 << 30, 16, 1 << 30, 1 << 30, 1 << 30, 1 << 30, 256, 1 << 40,
+                                    None) == _lib.EDM_ERR_CAPACITY
     assert native_lib.edm_set_timeout_ms(0) == _lib.EDM_ERR_BAD_ARG
     out = C.c_void_p()
     assert native_lib.edm_comm_create(3, 2, 1 << 20, 1 << 20, C.byref(out)) == _lib.EDM_ERR_BAD_ARG

@@ -31,7 +31,7 @@ def test_schedule_candidates_round_trip(native_lib):
 
 def test_measured_graph_and_descriptors_round_trip(tmp_path):
     spec = lowering.TPLinearSpec("ag_gemm", M=8192, N=1280, K=8192, world=8)
-    g = lowering.measured_graph(spec, lowering.Schedule(1, 2), total_us=355.0, gemm_only_us=130.0, tp_rank=0,
+    g = lowering.measured_graph(spec, lowering.Schedule(index=1, chunks=2, transport="ce"), total_us=355.0, gemm_only_us=130.0, tp_rank=0,
                                 device="B200", iteration=4)
     b = EDMBuilder(default_phase="decode")
     u = b.uop(irops.MOVEMENT_COPY, "kv.transfer", 0.0, 18.0,

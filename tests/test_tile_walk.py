@@ -22,7 +22,7 @@ def _blocks(M, N, tile_m, tile_n):
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 @pytest.mark.parametrize("op", ["gemm", "gemm_rs", "gemm_ar", "ag_gemm"])
 def test_every_tile_once_and_ranks_agree(native_lib, op, world, tile_m):
-    for (M, N), band, units in itertools.product(SHAPES, (0, 8), (1, 37, 148)):
+    for (M, N), (band, cols), units in itertools.product(SHAPES, ((0, 0), (8, 0), (8, 9), (4, 3), (0, 5)), (1, 37, 148)):
         if op == "gemm" and world > 1:
             continue
         if op == "gemm_rs" and (M % world or (M // world) % tile_m):
@@ -30,7 +30,7 @@ def test_every_tile_once_and_ranks_agree(native_lib, op, world, tile_m):
         mb, nb = _blocks(M, N, tile_m, 256)
         owners: dict = {}
         for rank in range(world):
-            walk = symm.tile_walk(op, rank, world, M, N, tile_m, 256, band, units)
+            walk = symm.tile_walk(op, rank, world, M, N, tile_m, 256, band, units, cols)
             tiles = [(m, n) for m, n, _, _ in walk if m >= 0]
             assert sorted(tiles) == sorted(itertools.product(range(mb), range(nb))), (op, world, M, N, rank)
             if op == "gemm_ar" and world > 1:
