@@ -1,24 +1,32 @@
 """Benchmark of the fused tensor-parallel linear path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens M]
+                    [--schedule qkv=IDX,gate_up=IDX] [--no-configs] [--quick]
 
-Workload (one "step" = one layer): the four linears of a Llama-3-70B prefill layer with the
-per-rank extents of tensor parallelism 8 -- all-gather+GEMM for QKV (N=1280) and gate_up
+Headline workload (one "step" = one layer): the four linears of a Llama-3-70B prefill layer with
+the per-rank extents of tensor parallelism 8 -- all-gather+GEMM for QKV (N=1280) and gate_up
 (N=7168) with K=8192, GEMM+reduce-scatter for o_proj (K=1024) and down_proj (K=3584) with
 N=8192 -- on M tokens (default 8192), bf16 with fp32 accumulation, synthetic inputs
 (activations ~N(0,1), weights ~N(0,0.02)).  On N GPUs the same per-rank extents run with the
 exchange across N ranks (weak scaling; N=8 is the reference configuration itself); on 1 GPU
-there is nothing to exchange and the step is the four GEMMs.
+there is nothing to exchange and the step is the four GEMMs.  Every launch runs the schedule the
+cost model selects for its shape (``lowering.select_schedule``); ``per_op`` reports that schedule
+and the model's prediction next to the measurement.
 
 Prints ONE JSON line on rank 0.  ``value`` is microseconds per layer, device-timed with CUDA
 events on the launching stream, maximum over ranks.  ``e2e`` is the same layer driven through
 the public operators from pinned host buffers: host->device copies of the step's activations
 and device->host copies of its outputs are inside the timed region (weights are parameters
 and stay resident); ``edmir_b200.host_io.HostStaging`` keeps uploads, kernels and downloads on
-three streams, and a step ends when all its results are in host memory.
+three streams, and a step ends when all its results are in host memory.  ``parity`` is a check,
+outside every timed region, of each launch's output on sampled rows against the float64 CPU
+oracle (the inputs of the other ranks come over the process group); the process exits non-zero
+when it fails.  ``configs`` holds the other shapes of the configuration list: the layer at 4096
+and 16384 tokens, the Llama-3-8B gate_up (all-gather+GEMM) and down_proj (GEMM+all-reduce at
+1..8192 tokens) at the run's TP, each with its roofline and the term that binds it.
 
 ``--impl reference`` times the CPU restatement of the path (the oracle; the reference itself
-has no implementation of it) on the host cores instead.
+has no implementation of it) on the host cores instead: whole layers, ``--steps`` of them.
 """
 from __future__ import annotations
 
@@ -46,8 +54,9 @@ NVLINK_GBS_NOMINAL = 900.0
 JSON_OUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch (gate_up, 55 % of the layer's
-# flops), from the ncu capture summarised in profiles/tp_gemm_bf16_layer_1gpu.md
+# flops), from the committed ncu summary of this kernel on this workload
 NCU_TRAFFIC_BYTES_GATE_UP = 1_080_005_000 + 111_048_960
+BF16_TOL = 1e-2
 
 
 def load_peaks():
@@ -65,10 +74,24 @@ def op_flops(M, K, N):
 
 
 def nvlink_bytes(op, M, K, N, world):
+    """Bytes per GPU and direction, bf16 on the wire."""
     if world <= 1:
         return 0.0
     frac = (world - 1) / world
-    return frac * M * (K if op == "ag_gemm" else N) * 2.0
+    if op == "ag_gemm":
+        return frac * M * K * 2.0
+    if op == "gemm_ar":
+        return 2.0 * frac * M * N * 2.0
+    return frac * M * N * 2.0
+
+
+def roofline_of(op, M, K, N, world, peaks):
+    """max(compute, HBM, NVLink) in microseconds and the name of the binding term."""
+    terms = {"tensor": op_flops(M, K, N) / (peaks["bf16_tflops"] * 1e12),
+             "hbm": 2.0 * (M * K + K * N + M * N) / (peaks["hbm_gbs"] * 1e9),
+             "nvlink": nvlink_bytes(op, M, K, N, world) / (NVLINK_GBS_NOMINAL * 1e9)}
+    bind = max(terms, key=terms.get)
+    return terms[bind] * 1e6, bind
 
 
 # ------------------------------------------------------------------ clocks
@@ -115,23 +138,28 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU arm (oracle port)
-def cpu_layer_us(M: int, sample_rows: int, threads: int) -> tuple[float, str]:
-    """One rank's four GEMMs of the layer on the host cores (fp32 torch CPU matmul over bf16-rounded
-    inputs, i.e. the oracle's arithmetic at the speed of the host BLAS), timed on `sample_rows` of
-    the M tokens and scaled to M."""
-    import torch
+class CpuLayer:
+    """One rank's four GEMMs of the layer on the host cores: fp32 torch CPU matmul over
+    bf16-rounded inputs, i.e. the oracle's arithmetic at the speed of the host BLAS."""
 
-    torch.set_num_threads(threads)
-    gen = torch.Generator(device="cpu").manual_seed(1234)
-    total = 0.0
-    for _name, _op, K, N in LAYER_OPS:
-        a = torch.randn(sample_rows, K, generator=gen).bfloat16().float()
-        b = (torch.randn(N, K, generator=gen) * 0.02).bfloat16().float()
-        torch.matmul(a[:64], b.t())  # warm the BLAS threads
+    def __init__(self, M: int, threads: int):
+        import torch
+
+        torch.set_num_threads(threads)
+        gen = torch.Generator(device="cpu").manual_seed(1234)
+        self.ops = []
+        for _name, _op, K, N in LAYER_OPS:
+            a = torch.randn(M, K, generator=gen).bfloat16().float()
+            b = (torch.randn(N, K, generator=gen) * 0.02).bfloat16().float().t().contiguous()
+            self.ops.append((a, b, torch.empty(M, N)))
+        self.torch = torch
+        self.M = M
+
+    def step_us(self) -> float:
         t0 = time.perf_counter()
-        torch.matmul(a, b.t())
-        total += time.perf_counter() - t0
-    return total * 1e6 * (M / sample_rows), f"{sample_rows} of {M} token rows, 4 GEMMs, fp32 CPU matmul, scaled x{M / sample_rows:g}"
+        for a, b, out in self.ops:
+            self.torch.matmul(a, b, out=out)
+        return (time.perf_counter() - t0) * 1e6
 
 
 def selector_sweep_us() -> float:
@@ -152,21 +180,20 @@ def run_reference(args) -> None:
         return
     threads = os.cpu_count() or 1
     M = args.tokens
-    sample = min(M, 1024)
-    for _ in range(max(args.warmup, 0) and 1):
-        cpu_layer_us(M, 128, threads)
-    vals = []
-    for _ in range(max(1, min(args.steps, 5))):
-        v, desc = cpu_layer_us(M, sample, threads)
-        vals.append(v)
-    value = statistics.median(vals)
+    layer = CpuLayer(M, threads)
+    for _ in range(args.warmup):
+        layer.step_us()
+    vals = [layer.step_us() for _ in range(args.steps)]
+    value = sum(vals) / len(vals)
+    desc = f"{args.steps} whole layers of {M} token rows (4 GEMMs each), fp32 CPU matmul, {threads} threads"
     line = {
-        "impl": "reference", "metric": "fused_tp_layer_time", "value": value, "unit": "us/layer",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3,
+        "impl": "reference", "metric": "fused_tp_layer_time", "value": round(value, 1), "unit": "us/layer",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(value / 1e3, 3),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(M, args.gpus),
-        "cpu_baseline": {"value": value, "unit": "us/layer", "cores": threads, "kind": "port", "sample": desc},
-        "e2e": {"value": value, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": round(value, 1), "unit": "us/layer", "cores": threads, "kind": "port", "sample": desc,
+                         "min_us": round(min(vals), 1), "max_us": round(max(vals), 1)},
+        "e2e": {"value": round(value, 1), "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), file=JSON_OUT, flush=True)
@@ -180,11 +207,21 @@ def workload_config(M: int, world: int) -> dict:
 
 
 # ------------------------------------------------------------------ GPU arm
+def parse_forced(text: str) -> dict:
+    out = {}
+    for item in filter(None, (text or "").split(",")):
+        name, _, idx = item.partition("=")
+        out[name.strip()] = int(idx)
+    return out
+
+
 def run_ours(args) -> None:
+    import numpy as np
     import torch
     import torch.distributed as dist
 
-    from edmir_b200 import host_io, linear, symm
+    from edmir_b200 import host_io, linear, lowering, symm
+    from edmir_b200.calibration import Calibration
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -196,11 +233,25 @@ def run_ours(args) -> None:
     M = args.tokens
     assert M % (128 * max(world, 1)) == 0, "tokens must split into 128-row blocks per rank"
     peaks, peak_src = load_peaks()
+    calib = Calibration.load()
+    forced = parse_forced(args.schedule)
+    with_configs = not (args.no_configs or args.quick)
+    big_m = max(M, 16384) if with_configs else M
 
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
     ctx = None
     if world > 1:
-        ctx = symm.SymmetricContext.create(symm.default_window_bytes(M, HIDDEN, HIDDEN, world), 1 << 20)
+        heap = 8192 * 4096 * 2 + (1 << 20) if with_configs else 1 << 20
+        ctx = symm.SymmetricContext.create(symm.default_window_bytes(big_m, HIDDEN, HIDDEN, world) // 2 + (64 << 20), heap)
+
+    def pick(name: str, op: str, m: int, K: int, N: int):
+        """(schedule, predicted us, launcher factory) for one op at this run's world size."""
+        spec = lowering.TPLinearSpec(op, m, N, K, world)
+        sel = lowering.select_schedule(spec, calib, tp_rank=rank)
+        idx = forced.get(name, sel.chosen)
+        sched = sel.schedules[idx]
+        assert sched.fused or world == 1, "the benchmark times fused launches; the unfused sequence is timed beside them"
+        return spec, sched, sel.costs[idx].makespan / 1e3, lowering.lower(spec, ctx, sched)
 
     ops = []
     for name, op, K, N in LAYER_OPS:
@@ -208,17 +259,14 @@ def run_ours(args) -> None:
         rows_out = M // world if op == "gemm_rs" else M
         a_host = torch.randn(rows_in, K, generator=gen).to(torch.bfloat16).pin_memory()
         b = (torch.randn(N, K, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+        spec, sched, predicted, fn = pick(name, op, M, K, N)
         ops.append({"name": name, "op": op, "K": K, "N": N, "a_host": a_host, "a": a_host.to(dev), "b": b,
                     "out": torch.empty(rows_out, N, dtype=torch.bfloat16, device=dev),
-                    "out_host": torch.empty(rows_out, N, dtype=torch.bfloat16).pin_memory()})
+                    "out_host": torch.empty(rows_out, N, dtype=torch.bfloat16).pin_memory(),
+                    "spec": spec, "sched": sched, "predicted_us": predicted, "fn": fn})
 
     def launch(o):
-        if world == 1:
-            linear.gemm(o["a"], o["b"], o["out"])
-        elif o["op"] == "ag_gemm":
-            ctx.ag_gemm(o["a"], o["b"], o["out"], chunks=args.chunks, transport=args.transport)
-        else:
-            ctx.gemm_rs(o["a"], o["b"], o["out"])
+        o["fn"](o["a"], o["b"], o["out"])
 
     def layer():
         for o in ops:
@@ -247,6 +295,16 @@ def run_ours(args) -> None:
             ms = float(t.item())
         return ms / steps * 1e3  # us per call
 
+    def op_record(name, op, m, K, N, us, sched=None, predicted=None):
+        fl = op_flops(m, K, N)
+        roof_us, bind = roofline_of(op, m, K, N, world, peaks)
+        rec = {"name": name, "op": op if world > 1 else "gemm", "tokens": m, "K": K, "N": N, "us": round(us, 2),
+               "tflops": round(fl / us / 1e6, 1), "roofline_us": round(roof_us, 2),
+               "roofline_frac": round(roof_us / us, 4), "binds": bind}
+        if sched is not None and world > 1:
+            rec.update({"schedule_index": sched.index, "schedule": sched.label(), "predicted_us": round(predicted, 1)})
+        return rec
+
     sampler = ClockSampler(local) if rank == 0 else None
     layer_us = timed(layer, args.steps, max(args.warmup, 3))
 
@@ -255,13 +313,7 @@ def run_ours(args) -> None:
     sub_steps = max(10, args.steps // 4)
     for o in ([] if args.quick else ops):
         us = timed(lambda o=o: launch(o), sub_steps, 3)
-        fl = op_flops(M, o["K"], o["N"])
-        wire = nvlink_bytes(o["op"], M, o["K"], o["N"], world)
-        roof_us = max(fl / (peaks["bf16_tflops"] * 1e12), wire / (NVLINK_GBS_NOMINAL * 1e9)) * 1e6
-        per_op.append({"name": o["name"], "op": o["op"] if world > 1 else "gemm", "us": round(us, 2),
-                       "tflops": round(fl / us / 1e6, 1), "roofline_us": round(roof_us, 2),
-                       "roofline_frac": round(roof_us / us, 4),
-                       "binds": "nvlink" if wire / (NVLINK_GBS_NOMINAL * 1e9) > fl / (peaks["bf16_tflops"] * 1e12) else "tensor"})
+        per_op.append(op_record(o["name"], o["op"], M, o["K"], o["N"], us, o["sched"], o["predicted_us"]))
 
     # comparison baselines measured in the same run
     extra = {}
@@ -305,7 +357,109 @@ def run_ours(args) -> None:
     else:
         extra["cublas_matmul_us"] = round(timed(unfused_layer, sub_steps, 3), 2)
 
-    # end to end from pinned host buffers
+    # ---------------------------------------------------------------- parity (outside every timed region)
+    def verify() -> dict:
+        """Each launch's output on sampled rows against the float64 oracle.  Rows and operands of
+        the other ranks travel over the process group (the checker may use a library collective)."""
+        from oracle import tp_linear as oracle
+
+        npf = lambda t: t.float().cpu().numpy()
+        worst, checked = 0.0, 0
+        for o in ops:
+            o["out"].fill_(float("nan"))
+            if ctx is not None:
+                sync_all()
+                ctx.poison()
+                sync_all()
+            launch(o)
+            sync_all()
+            if o["op"] == "ag_gemm" or world == 1:
+                rows_in = o["a"].shape[0]
+                idx = torch.unique(torch.cat([torch.arange(0, min(8, rows_in)), torch.arange(max(rows_in - 8, 0), rows_in),
+                                              torch.randint(0, rows_in, (16,), generator=torch.Generator().manual_seed(7))]))
+                mine = o["a"][idx.to(dev)].contiguous()
+                if world > 1 and o["op"] == "ag_gemm":
+                    parts = [torch.empty_like(mine) for _ in range(world)]
+                    dist.all_gather(parts, mine)
+                    x = torch.cat(parts, 0)
+                    grows = torch.cat([idx + r * rows_in for r in range(world)])
+                    got = o["out"][grows.to(dev)]
+                    want = oracle.gemm(npf(x), npf(o["b"]))
+                else:
+                    got = o["out"][idx.to(dev)]
+                    want = oracle.gemm(npf(mine), npf(o["b"]))
+            else:  # gemm_rs: my rows of the sum over ranks of A_s @ B_s^T
+                rows_out = M // world
+                idx = torch.unique(torch.cat([torch.arange(0, 4), torch.arange(rows_out - 4, rows_out),
+                                              torch.randint(0, rows_out, (8,), generator=torch.Generator().manual_seed(11))]))
+                all_rows = torch.cat([idx + r * rows_out for r in range(world)]).to(dev)
+                mine = o["a"][all_rows].contiguous()           # my A at every rank's sampled rows
+                a_parts = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(a_parts, mine)
+                b_parts = [torch.empty_like(o["b"]) for _ in range(world)]
+                dist.all_gather(b_parts, o["b"])
+                lo, hi = rank * len(idx), (rank + 1) * len(idx)
+                want = None
+                for s in range(world):
+                    part = oracle.gemm(npf(a_parts[s][lo:hi]), npf(b_parts[s]))
+                    want = part if want is None else want + part
+                got = o["out"][idx.to(dev)]
+                del a_parts, b_parts
+            err = oracle.rel_l2(npf(got), want)
+            worst = max(worst, err if np.isfinite(err) else float("inf"))
+            checked += got.shape[0]
+        if world > 1:
+            t = torch.tensor([worst if np.isfinite(worst) else 1e30], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            worst = float(t.item())
+        return {"max_rel_l2": float(f"{worst:.3e}"), "tolerance": BF16_TOL, "ok": bool(worst <= BF16_TOL),
+                "rows_checked_per_rank": checked, "what": "every op of the layer, sampled rows, float64 CPU oracle; "
+                "windows and outputs NaN-filled before the checked launch"}
+
+    parity = None if args.quick else verify()
+
+    # ---------------------------------------------------------------- the other configurations
+    configs = []
+    if with_configs:
+        def device_op(op, m, K, N):
+            rows_in = m // world if op == "ag_gemm" else m
+            a = torch.randn(rows_in, K, device=dev).to(torch.bfloat16)
+            b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+            return a, b
+        def time_op(name, op, m, K, N, out=None):
+            if op != "gemm_ar" and m % (128 * world):
+                return None
+            a, b = device_op(op, m, K, N)
+            spec, sched, predicted, fn = pick(name, op, m, K, N)
+            if out is None:
+                rows_out = m // world if op == "gemm_rs" else m
+                out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=dev)
+            us = timed(lambda: fn(a, b, out), 10, 3)
+            return op_record(name, op, m, K, N, us, sched, predicted)
+        for m in (4096, 16384):
+            if m == M:
+                continue
+            recs = [time_op(name, op, m, K, N) for name, op, K, N in LAYER_OPS]
+            if all(recs):
+                configs.append({"config": f"llama3-70b layer, tp8-local extents, {m} tokens", "ops": recs,
+                                "layer_us": round(sum(r["us"] for r in recs), 2)})
+        if world > 1:
+            rec = time_op("8b_gate_up", "ag_gemm", 8192, 4096, 2 * 14336 // world)
+            if rec:
+                configs.append({"config": f"llama3-8b gate_up, all-gather+GEMM, tp{world}", "ops": [rec]})
+        ar_out = ctx.empty((8192, 4096), torch.bfloat16) if ctx is not None else None
+        recs = []
+        for m in (1, 16, 128, 1024, 8192):
+            if world > 1:
+                recs.append(time_op("8b_down", "gemm_ar", m, 14336 // world, 4096, out=ar_out[:m]))
+            else:
+                a, b = device_op("gemm", m, 14336, 4096)
+                out = torch.empty(m, 4096, dtype=torch.bfloat16, device=dev)
+                recs.append(op_record("8b_down", "gemm", m, 14336, 4096, timed(lambda: linear.gemm(a, b, out), 10, 3)))
+        configs.append({"config": f"llama3-8b down_proj, GEMM+all-reduce, tp{world}", "ops": [r for r in recs if r]})
+        torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- end to end from pinned host buffers
     staging = host_io.HostStaging(dev)
     def e2e_step():
         # uploads, kernels and downloads on three streams; the step ends (on the timed stream)
@@ -349,13 +503,22 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * len(ops),
             "clocks": clocks,
+            "parity": parity,
         }
+        if clocks and clocks.get("sm_mhz") and layer_us:
+            # time x clock: comparable between runs whose boards were granted different clocks
+            line["value_us_x_ghz"] = round(layer_us * clocks["sm_mhz"] / 1e3, 1)
         line.update(extra)
+        if configs:
+            line["configs"] = configs
         if world == 1 and not args.no_cpu and not args.quick:
             threads = os.cpu_count() or 1
-            v, desc = cpu_layer_us(M, min(M, 1024), threads)
-            line["cpu_baseline"] = {"value": round(v, 1), "unit": "us/layer", "cores": threads, "kind": "port",
-                                    "sample": desc, "selector_sweep_us": round(selector_sweep_us(), 1)}
+            cpu = CpuLayer(M, threads)
+            cpu.step_us()
+            vals = [cpu.step_us() for _ in range(3)]
+            line["cpu_baseline"] = {"value": round(sum(vals) / len(vals), 1), "unit": "us/layer", "cores": threads,
+                                    "kind": "port", "sample": f"3 whole layers of {M} token rows (4 GEMMs each), "
+                                    f"fp32 CPU matmul, {threads} threads", "selector_sweep_us": round(selector_sweep_us(), 1)}
         print(json.dumps(line), file=JSON_OUT, flush=True)
 
     if ctx is not None:
@@ -363,6 +526,8 @@ def run_ours(args) -> None:
         ctx.close()
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.exit(f"parity check failed: {parity}")
 
 
 def _claim_stdout():
@@ -383,14 +548,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--tokens", type=int, default=8192)
-    ap.add_argument("--chunks", type=int, default=1, help="all-gather chunks per shard")
-    ap.add_argument("--transport", default="ce", choices=("sm", "ce"),
-                    help="all-gather shards by in-kernel stores (sm) or copy engines (ce)")
+    ap.add_argument("--schedule", default="", help="force schedule candidates by index, e.g. qkv=3,gate_up=12 "
+                                                   "(indices as printed by examples/select_schedule.py)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-configs", action="store_true", help="time the headline layer only")
     ap.add_argument("--quick", action="store_true",
-                    help="time the layer only (no per-op, baseline, end-to-end or CPU legs): for profiler runs")
+                    help="time the layer only (no per-op, baseline, parity, end-to-end or CPU legs): for profiler runs")
     args = ap.parse_args()
     if args.impl == "reference":
+        if args.steps == 200:
+            args.steps, args.warmup = 20, min(args.warmup, 2)  # whole CPU layers take ~1.3 s each
         run_reference(args)
     else:
         run_ours(args)

@@ -59,6 +59,20 @@ class TpCall(C.Structure):
     ]
 
 
+class MoeCall(C.Structure):
+    """``edm_moe_call_t``."""
+
+    _fields_ = [
+        ("tokens", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32), ("experts", C.c_int32),
+        ("x", C.c_void_p), ("ldx", C.c_int64),
+        ("logits", C.c_void_p), ("ld_logits", C.c_int64),
+        ("w1", C.c_void_p), ("ldw1", C.c_int64),
+        ("w2", C.c_void_p), ("ldw2", C.c_int64),
+        ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 class CostParams(C.Structure):
     """``edm_cost_params_t``."""
 
@@ -114,6 +128,11 @@ SIGNATURES = {
     "edm_gemm_rs_bf16": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_gemm_ar_bf16": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "edm_ag_gemm_bf16": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "edm_moe_window_bytes": (_sz, [_i64, _i64, _i64, C.c_int]),
+    "edm_moe_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, C.c_int]),
+    "edm_moe_routing_offsets": (C.c_int, [_i64, _i64, _i64, _i64, C.c_int, C.POINTER(_sz)]),
+    "edm_moe_forward": (C.c_int, [_vp, C.POINTER(MoeCall), _vp]),
+    "edm_moe_forward_emulated": (C.c_int, [C.POINTER(_vp), C.POINTER(MoeCall), C.c_int, _vp]),
     "edm_schedule_cost": (C.c_int, [C.POINTER(CostParams), _i32, C.POINTER(CandidateCost)]),
     "edm_graph_cost": (C.c_int, [_i32, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(C.c_uint8), _i32,
                                  C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i64), C.POINTER(_i64),

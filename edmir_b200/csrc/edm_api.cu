@@ -11,6 +11,7 @@
 
 #include "../../include/edm_b200.h"
 #include "tp_gemm.cuh"
+#include "moe.cuh"
 
 using namespace edm;
 
@@ -97,6 +98,9 @@ void dbg_add_matrix(const void* p, int64_t rows, int64_t cols, int64_t ld, int e
   if (rows > 0) g_dbg.add(p, (static_cast<size_t>(rows - 1) * ld + cols) * elem);
 }
 int dbg_publish(cudaStream_t s) {
+  // the table is uploaded and awaited per launch: not possible while the stream is being captured
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone) return EDM_ERR_UNSUPPORTED;
   void* p = nullptr;
   // the library's own device arrays
   if (cudaGetSymbolAddress(&p, g_tail_scratch) == cudaSuccess) g_dbg.add(p, sizeof(g_tail_scratch));
@@ -425,7 +429,7 @@ ScratchGuard* scratch_guard() {
 // Would the kernel cut tiles of this launch along K?  Mirrors the condition in tp_gemm_kernel.
 bool launch_splits(const LaunchParams& lp, const RankParams& P, int dtype, int cg, int bn, int grid) {
   if (dtype != EDM_DTYPE_BF16 || bn != kBlockN || P.passes != 1 || grid > kTailMaxCtas) return false;
-  if (P.mode != kPlain && P.mode != kAG) return false;
+  if ((P.mode != kPlain && P.mode != kAG) || P.group_table != nullptr) return false;
   const int pushers = (P.mode == kAG && P.world > 1 && !P.ag_external) ? lp.pusher_ctas : 0;
   const int units = (lp.ctas_per_vrank - pushers) / cg;
   const int64_t tiles = ((static_cast<int64_t>(P.M) + kBlockM * cg - 1) / (kBlockM * cg)) *
@@ -1164,6 +1168,210 @@ int edm_ag_gemm_bf16(edm_comm_t* comm, const void* x, int64_t ldx, const void* w
                      void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, int32_t chunks,
                      void* stream) {
   return tp_bf16(comm, EDM_OP_AG_GEMM, x, ldx, w, ldw, d, ldd, M, N, K, chunks, stream);
+}
+
+}  // extern "C"
+
+// ======================================================================== mixture of experts
+namespace {
+
+struct MoeLayout {
+  int W, E_local, C, max_blocks;
+  // window (inside the parity half)
+  size_t w_counts, w_xbuf, w_meta, w_cbuf, window_need;
+  // workspace
+  size_t s_idx, s_w, s_slot, s_tgu, s_tdn, s_nblk, s_ctr, s_y, s_act, s_z, workspace_need;
+};
+
+int moe_layout(int64_t T, int64_t H, int64_t F, int64_t E, int W, MoeLayout& L) {
+  if (T < 1 || H < 8 || F < 8 || E < 2 || W < 1 || W > EDM_MAX_RANKS) return EDM_ERR_BAD_ARG;
+  if (E > kMoeMaxExperts || E % W || H % 8 || F % 8) return EDM_ERR_BAD_ARG;
+  if (T > (1 << 22) || H > (1 << 20) || F > (1 << 20)) return EDM_ERR_BAD_ARG;
+  L.W = W;
+  L.E_local = static_cast<int>(E / W);
+  L.C = static_cast<int>(align_up(static_cast<size_t>(T) * W, 256));  // a token sends at most one row to an expert
+  L.max_blocks = L.E_local * (L.C / 256);
+  const size_t rows = static_cast<size_t>(L.E_local) * L.C;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { const size_t at = o; o = align_up(o + bytes, 256); return at; };
+  L.w_counts = take(static_cast<size_t>(W) * E * 4);
+  L.w_xbuf = take(rows * H * 2);
+  L.w_meta = take(rows * 4);
+  L.w_cbuf = take(static_cast<size_t>(T) * 2 * H * 2);
+  L.window_need = o;
+  o = 0;
+  L.s_idx = take(static_cast<size_t>(T) * 2 * 4);
+  L.s_w = take(static_cast<size_t>(T) * 2 * 4);
+  L.s_slot = take(static_cast<size_t>(T) * 2 * 4);
+  L.s_tgu = take(static_cast<size_t>(L.max_blocks) * 16);
+  L.s_tdn = take(static_cast<size_t>(L.max_blocks) * 16);
+  L.s_nblk = take(4);
+  L.s_ctr = take(8);
+  L.s_y = take(rows * 2 * F * 2);
+  L.s_act = take(rows * F * 2);
+  L.s_z = take(rows * H * 2);
+  L.workspace_need = o;
+  return EDM_OK;
+}
+
+// One launch of the GEMM kernel over the row blocks an earlier kernel listed in `table`.
+int grouped_gemm(const void* a, int64_t lda, int64_t a_rows, const void* b, int64_t ldb, int64_t b_rows, void* d,
+                 int64_t ldd, int64_t N, int64_t K, const int32_t* table, const int32_t* count, int max_blocks,
+                 cudaStream_t s) {
+  LaunchParams lp;
+  std::memset(&lp, 0, sizeof(lp));
+  RankParams& P = lp.r[0];
+  const int cg = 2;
+  int rc;
+  if ((rc = make_tmap(&P.tmap_a[0], a, a_rows, K, lda, 2, kBlockM))) return rc;
+  if ((rc = make_tmap(&P.tmap_b[0], b, b_rows, K, ldb, 2, kBlockN / cg))) return rc;
+  P.tmap_a[1] = P.tmap_a[0];
+  P.tmap_b[1] = P.tmap_b[0];
+  P.passes = 1;
+  P.M = max_blocks * kBlockM * cg;
+  P.N = static_cast<int32_t>(N); P.K = static_cast<int32_t>(K);
+  P.rank = 0; P.world = 1; P.mode = kPlain; P.epoch = 1;
+  P.out = d; P.ld_out = ldd;
+  P.group_table = table; P.group_count = count;
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  int resident = 0;
+  if ((rc = max_resident_ctas(EDM_DTYPE_BF16, cg, sms, &resident))) return rc;
+  apply_tuning(lp, s);
+  lp.tail_split = 0;  // row blocks come from a device-side table: no split of a last wave
+  lp.num_vranks = 1;
+  lp.ctas_per_vrank = resident;
+  lp.timeout_ns = g_timeout_ns;
+  lp.profile = g_profile;
+  return launch_variant(EDM_DTYPE_BF16, cg, kBlockN, lp, resident, false, s);
+}
+
+int moe_forward_impl(edm_comm_t* const* comms, const edm_moe_call_t* calls, int n, cudaStream_t s) {
+  MoeParams mp;
+  std::memset(&mp, 0, sizeof(mp));
+  mp.num_vranks = n;
+  mp.timeout_ns = g_timeout_ns;
+  MoeLayout L[kMaxVirtualRanks];
+  dbg_reset();
+  for (int i = 0; i < n; ++i) {
+    edm_comm* c = comms[i];
+    const edm_moe_call_t& call = calls[i];
+    if (!c || !call.x || !call.logits || !call.w1 || !call.w2 || !call.out || !call.workspace) return EDM_ERR_BAD_ARG;
+    const int W = c->world;
+    for (int p = 0; p < W; ++p)
+      if (!c->base[p]) return EDM_ERR_BAD_ARG;
+    int rc = moe_layout(call.tokens, call.hidden, call.ffn, call.experts, W, L[i]);
+    if (rc) return rc;
+    if (call.tokens != calls[0].tokens || call.hidden != calls[0].hidden || call.ffn != calls[0].ffn ||
+        call.experts != calls[0].experts)
+      return EDM_ERR_BAD_ARG;
+    if (L[i].window_need > c->window_bytes / 2 || static_cast<size_t>(3 * W) * 4 > c->flag_bytes / 2)
+      return EDM_ERR_CAPACITY;
+    if (call.workspace_bytes < L[i].workspace_need) return EDM_ERR_CAPACITY;
+    if ((reinterpret_cast<uintptr_t>(call.workspace) & 255u) || (reinterpret_cast<uintptr_t>(call.x) & 15u) ||
+        (reinterpret_cast<uintptr_t>(call.out) & 15u) || ((call.ldx * 2) & 15) || ((call.ldo * 2) & 15) ||
+        call.ldx < call.hidden || call.ldo < call.hidden || call.ld_logits < call.experts ||
+        call.ldw1 < call.hidden || call.ldw2 < call.ffn)
+      return EDM_ERR_BAD_ARG;
+    MoeRank& R = mp.r[i];
+    R.T = call.tokens; R.H = call.hidden; R.F = call.ffn; R.E = call.experts;
+    R.E_local = L[i].E_local; R.W = W; R.rank = c->rank; R.C = L[i].C; R.max_blocks = L[i].max_blocks;
+    const uint32_t epoch = c->epoch + 1;
+    R.epoch = epoch;
+    const size_t par = epoch & 1u;
+    R.x = static_cast<const __nv_bfloat16*>(call.x); R.ld_x = call.ldx;
+    R.logits = call.logits; R.ld_logits = call.ld_logits;
+    R.out = static_cast<__nv_bfloat16*>(call.out); R.ld_out = call.ldo;
+    char* ws = static_cast<char*>(call.workspace);
+    R.topk_idx = reinterpret_cast<int32_t*>(ws + L[i].s_idx);
+    R.topk_w = reinterpret_cast<float*>(ws + L[i].s_w);
+    R.slot = reinterpret_cast<int32_t*>(ws + L[i].s_slot);
+    R.table_gu = reinterpret_cast<int32_t*>(ws + L[i].s_tgu);
+    R.table_dn = reinterpret_cast<int32_t*>(ws + L[i].s_tdn);
+    R.n_blocks = reinterpret_cast<int32_t*>(ws + L[i].s_nblk);
+    R.done_ctr = reinterpret_cast<uint32_t*>(ws + L[i].s_ctr);
+    R.Y = reinterpret_cast<const __nv_bfloat16*>(ws + L[i].s_y);
+    R.act = reinterpret_cast<__nv_bfloat16*>(ws + L[i].s_act);
+    R.Z = reinterpret_cast<const __nv_bfloat16*>(ws + L[i].s_z);
+    for (int p = 0; p < W; ++p) {
+      char* win = c->base[p] + c->off_window() + par * (c->window_bytes / 2);
+      R.counts[p] = reinterpret_cast<uint32_t*>(win + L[i].w_counts);
+      R.xbuf[p] = reinterpret_cast<__nv_bfloat16*>(win + L[i].w_xbuf);
+      R.meta[p] = reinterpret_cast<int32_t*>(win + L[i].w_meta);
+      R.cbuf[p] = reinterpret_cast<__nv_bfloat16*>(win + L[i].w_cbuf);
+      R.flags[p] = reinterpret_cast<uint32_t*>(c->base[p] + c->off_flags() + par * (c->flag_bytes / 2));
+      dbg_add(c->base[p], c->total_bytes);
+    }
+    dbg_add(call.workspace, call.workspace_bytes);
+    dbg_add_matrix(call.out, call.tokens, call.hidden, call.ldo, 2);
+    EDM_CUDA(cudaMemsetAsync(R.done_ctr, 0, 8, s));
+  }
+  if (int rc = dbg_publish(s)) return rc;
+  const int sms = num_sms();
+  if (sms <= 0) return EDM_ERR_CUDA;
+  const dim3 wide(static_cast<unsigned>(sms / n > 0 ? sms / n : 1), static_cast<unsigned>(n));
+  const dim3 one(1, static_cast<unsigned>(n));
+  moe_route_kernel<<<one, kMoeRouteThreads, 0, s>>>(mp);
+  moe_dispatch_kernel<<<wide, 256, 0, s>>>(mp);
+  moe_plan_kernel<<<one, 64, 0, s>>>(mp);
+  EDM_CUDA(cudaGetLastError());
+  for (int i = 0; i < n; ++i) {
+    const MoeRank& R = mp.r[i];
+    const int64_t rows = static_cast<int64_t>(R.E_local) * R.C;
+    int rc = grouped_gemm(R.xbuf[R.rank], R.H, rows, calls[i].w1, calls[i].ldw1, static_cast<int64_t>(R.E_local) * 2 * R.F,
+                          const_cast<__nv_bfloat16*>(R.Y), 2 * R.F, 2 * R.F, R.H, R.table_gu, R.n_blocks, R.max_blocks, s);
+    if (rc) return rc;
+  }
+  moe_silu_mul_kernel<<<wide, 256, 0, s>>>(mp);
+  EDM_CUDA(cudaGetLastError());
+  for (int i = 0; i < n; ++i) {
+    const MoeRank& R = mp.r[i];
+    const int64_t rows = static_cast<int64_t>(R.E_local) * R.C;
+    int rc = grouped_gemm(R.act, R.F, rows, calls[i].w2, calls[i].ldw2, static_cast<int64_t>(R.E_local) * R.H,
+                          const_cast<__nv_bfloat16*>(R.Z), R.H, R.H, R.F, R.table_dn, R.n_blocks, R.max_blocks, s);
+    if (rc) return rc;
+  }
+  moe_combine_kernel<<<wide, 256, 0, s>>>(mp);
+  moe_finish_kernel<<<wide, 256, 0, s>>>(mp);
+  EDM_CUDA(cudaGetLastError());
+  for (int i = 0; i < n; ++i) comms[i]->epoch += 1;
+  return EDM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t edm_moe_window_bytes(int64_t tokens, int64_t hidden, int64_t experts, int world) {
+  MoeLayout L;
+  if (moe_layout(tokens, hidden, 8, experts, world, L)) return 0;
+  return 2 * align_up(L.window_need, 1024);
+}
+size_t edm_moe_workspace_bytes(int64_t tokens, int64_t hidden, int64_t ffn, int64_t experts, int world) {
+  MoeLayout L;
+  if (moe_layout(tokens, hidden, ffn, experts, world, L)) return 0;
+  return L.workspace_need;
+}
+int edm_moe_routing_offsets(int64_t tokens, int64_t hidden, int64_t ffn, int64_t experts, int world, size_t out[3]) {
+  MoeLayout L;
+  if (!out) return EDM_ERR_BAD_ARG;
+  int rc = moe_layout(tokens, hidden, ffn, experts, world, L);
+  if (rc) return rc;
+  out[0] = L.s_idx; out[1] = L.s_w; out[2] = L.s_slot;
+  return EDM_OK;
+}
+int edm_moe_forward(edm_comm_t* comm, const edm_moe_call_t* call, void* stream) {
+  if (!comm || !call) return EDM_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (capturing(s)) return EDM_ERR_UNSUPPORTED;  // flags carry the context's call counter
+  edm_comm_t* comms[1] = {comm};
+  return moe_forward_impl(comms, call, 1, s);
+}
+int edm_moe_forward_emulated(edm_comm_t* const* comms, const edm_moe_call_t* calls, int n, void* stream) {
+  if (!comms || !calls || n < 1 || n > kMaxVirtualRanks) return EDM_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (capturing(s)) return EDM_ERR_UNSUPPORTED;
+  return moe_forward_impl(comms, calls, n, s);
 }
 
 }  // extern "C"

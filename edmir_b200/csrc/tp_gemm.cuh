@@ -116,6 +116,13 @@ struct alignas(64) RankParams {
   int32_t seg_kblocks;     // split-fp32: K blocks accumulated in TMEM before folding into scratch (0 = all)
   int32_t ag_external;     // AG: shards and chunk flags are delivered by copy engines, not by this kernel
   int32_t ag_ce_lo;        // AG: shards for peers rank-d with d >= ag_ce_lo come by copy engine, nearer ones are pushed by this kernel
+  // Grouped GEMM (PLAIN mode only; the experts of a mixture-of-experts layer): row block j of the
+  // walk reads A and writes D at row group_table[4j], reads B from row group_table[4j+1] on, and
+  // holds group_table[4j+2] valid rows; *group_count row blocks exist.  Both live in device memory
+  // and are written by an earlier kernel on the stream (how many rows each expert received is not
+  // known on the host).  M then only bounds the number of row blocks.
+  const int32_t* group_table;
+  const int32_t* group_count;
   void* peer_out[kMaxRanks];   // AR: every rank's output as mapped here
   char* win[kMaxRanks];        // every rank's window (parity half already selected)
   uint32_t* flags[kMaxRanks];  // every rank's flag array
@@ -268,8 +275,8 @@ struct TileWalk {
 
   // tile_m = rows of one scheduling tile: 128, or 256 when a CTA pair shares a tile
   // units = CTAs (or CTA pairs) walking the tiles concurrently
-  __device__ TileWalk(const RankParams& p, int tile_m, int tile_n, int band_rows, int units, int cols)
-      : TileWalk(p.mode, p.rank, p.world, p.M, p.N, tile_m, tile_n, band_rows, units, cols) {}
+  __device__ TileWalk(const RankParams& p, int rows, int tile_m, int tile_n, int band_rows, int units, int cols)
+      : TileWalk(p.mode, p.rank, p.world, rows, p.N, tile_m, tile_n, band_rows, units, cols) {}
   __host__ __device__ TileWalk(int mode_, int rank_, int world_, int M, int N, int tile_m, int tile_n,
                                int band_rows, int units, int cols = 0) {
     mode = mode_; rank = rank_; world = world_;
@@ -607,7 +614,23 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_slot);
 
-  const TileWalk walk(P, kBlockM * kCG, kBN, lp.band, num_ctas, lp.band_cols);
+  // grouped: as many row blocks as the table holds (read once; an earlier kernel wrote it)
+  const bool grouped = P.group_table != nullptr;
+  const int walk_rows = grouped ? min(__ldg(P.group_count) * kBlockM * kCG, P.M) : P.M;
+  const TileWalk walk(P, walk_rows, kBlockM * kCG, kBN, lp.band, num_ctas, lp.band_cols);
+  // first row of A / D, first row of B and valid rows of the 128-row half `half` of row block m_blk
+  auto block_rows = [&](int m_blk, int half, int& row0, int& b_row0, int& rows) {
+    if (grouped) {
+      const int4 e = __ldg(reinterpret_cast<const int4*>(P.group_table) + m_blk);
+      row0 = e.x + half * kBlockM;
+      b_row0 = e.y;
+      rows = max(0, min(kBlockM, e.z - half * kBlockM));
+    } else {
+      row0 = (m_blk * kCG + half) * kBlockM;
+      b_row0 = 0;
+      rows = min(kBlockM, P.M - row0);
+    }
+  };
   const int num_kb_pass = (P.K + kBlockK - 1) / kBlockK;
   // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation
   // drifts.  The split-fp32 path therefore accumulates `seg_kb` K blocks at a time in TMEM and
@@ -619,7 +642,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   // local tiles anyway; the split-fp32 path already uses its accumulator segments)
   const TailSplit tail(walk.positions, num_ctas, num_kb_pass,
                        (kBN == 256 && (P.mode == kPlain || P.mode == kAG) && P.passes == 1 && num_segs == 1 &&
-                        gridDim.x <= kTailMaxCtas) ? lp.tail_split : 0);
+                        !grouped && gridDim.x <= kTailMaxCtas) ? lp.tail_split : 0);
 
   // Work items of this CTA, in order: its whole tiles, then at most one claimed piece of a tail
   // tile.  `claim` is called once, when the whole tiles are done: the producer thread of the
@@ -1051,8 +1074,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         const int k_lo = w.k_lo, k_hi = w.k_hi;
         const Tile t = walk.at(w.pos);
         if (!t.valid) continue;
-        const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM;  // this CTA's rows of A
-        const int n0 = t.n_blk * kBN + static_cast<int>(pr) * (kBN / kCG);  // its rows of B
+        int m0, b_row0, rows_unused;  // this CTA's rows of A
+        block_rows(t.m_blk, static_cast<int>(pr), m0, b_row0, rows_unused);
+        const int n0 = b_row0 + t.n_blk * kBN + static_cast<int>(pr) * (kBN / kCG);  // its rows of B
         const CUtensorMap* amap = &P.tmap_a[0];
         int a_row = m0;
         if (P.mode == kAG) {
@@ -1384,9 +1408,10 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       // Where the tile goes.  Fused modes: every tile -- this rank's own included -- is shipped
       // as a partial into the owner's window slot [source rank][slot]; the owner's reducer warps
       // add the slots up.  Otherwise it is written to the output in place.
-      const int m0 = (t.m_blk * kCG + static_cast<int>(pr)) * kBlockM, n0 = t.n_blk * kBN;
+      int m0, b_row_unused, valid_rows;
+      block_rows(t.m_blk, static_cast<int>(pr), m0, b_row_unused, valid_rows);
+      const int n0 = t.n_blk * kBN;
       const int valid_cols = min(kBN, P.N - n0);
-      const int valid_rows = min(kBlockM, P.M - m0);
       char* dst_base;
       if (fused)
         dst_base = P.win[t.owner] + (static_cast<int64_t>(P.rank) * P.max_owned + slot_idx) * kTileOutBytes;

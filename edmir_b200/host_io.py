@@ -14,8 +14,10 @@ at the same time.  Ordering is by events only; nothing blocks the host.
     io.drain()                             # the caller's stream now waits for every download
 
 Hazards covered: a device operand is not overwritten by the next upload before the launch that
-reads it has finished; a device result is not overwritten by the next launch before its download
-has finished.  Host buffers belong to the caller, who must not touch ``out_host`` before a
+reads it has finished (nor, the first time a buffer is seen, before earlier work on the caller's
+stream has); a device result is not overwritten by the next launch before its download has
+finished.  The device buffers belong to the caller for as long as copies of them may be in flight:
+free or reuse them elsewhere only after a ``drain()`` and a synchronisation of the current stream.  Host buffers belong to the caller, who must not touch ``out_host`` before a
 ``drain()`` followed by a synchronisation of the current stream, nor rewrite ``a_host`` before
 the upload that reads it has run (``drain()`` also covers the uploads issued so far).
 """
@@ -47,10 +49,13 @@ class HostStaging:
         if a_host.shape != a_dev.shape or out_host.shape != out_dev.shape:
             raise ValueError("host and device buffers must have the same shapes")
         cur = torch.cuda.current_stream(self.device)
-        # upload: after the previous reader of a_dev, and after whatever the caller did before
+        # upload: after the previous reader of a_dev that went through this object; a buffer seen
+        # for the first time may still be in use by earlier work on the caller's stream
         ev = self._read_done.get(a_dev.data_ptr())
         if ev is not None:
             self.up.wait_event(ev)
+        else:
+            self.up.wait_stream(cur)
         with torch.cuda.stream(self.up):
             a_dev.copy_(a_host, non_blocking=True)
             uploaded = torch.cuda.Event()
@@ -80,3 +85,8 @@ class HostStaging:
             cur.wait_event(ev)
         if self._last_upload is not None:
             cur.wait_event(self._last_upload)
+        # forget buffers whose last use has already completed (the maps would otherwise grow with
+        # every distinct buffer ever passed in)
+        for table in (self._read_done, self._download_done):
+            for key in [k for k, ev in table.items() if ev.query()]:
+                del table[key]

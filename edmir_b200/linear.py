@@ -37,11 +37,17 @@ def prepare_weight(w_kn: torch.Tensor) -> torch.Tensor:
     return w_kn.t().contiguous()
 
 
+_gemm_bf16 = None  # the bound C entry point (attribute lookups on a CDLL cost microseconds per call)
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K]^T`` in bf16 with fp32 accumulation."""
-    _require_cuda(a, b)
-    _check_2d(a, "a")
-    _check_2d(b, "b")
+    global _gemm_bf16
+    if not (a.is_cuda and b.is_cuda):
+        raise ValueError("operands must be CUDA tensors (there is no CPU path)")
+    if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
+        _check_2d(a, "a")
+        _check_2d(b, "b")
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise ValueError("gemm expects bfloat16 operands")
     M, K = a.shape
@@ -51,13 +57,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> t
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     else:
-        _check_2d(out, "out")
-        if tuple(out.shape) != (M, N) or out.dtype != torch.bfloat16:
-            raise ValueError("out must be bfloat16 of shape [M, N]")
-    lib = _lib.load()
-    rc = lib.edm_gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),
-                           out.stride(0), M, N, K, _stream())
-    _lib.check(rc, "edm_gemm_bf16")
+        if out.dim() != 2 or out.stride(1) != 1:
+            _check_2d(out, "out")
+        if out.shape[0] != M or out.shape[1] != N or out.dtype != torch.bfloat16 or not out.is_cuda:
+            raise ValueError("out must be a bfloat16 CUDA tensor of shape [M, N]")
+    if _gemm_bf16 is None:
+        _gemm_bf16 = _lib.load().edm_gemm_bf16
+    rc = _gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+                    _stream())
+    if rc:
+        _lib.check(rc, "edm_gemm_bf16")
     return out
 
 

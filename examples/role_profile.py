@@ -1,7 +1,8 @@
 """Per-role device time of the fused launches (where a launch spends its time).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
-        --master-port 29530 -m edmir_b200.role_profile [--tokens 8192] [--chunks 2] [--transport sm|ce] [--probe]
+        --master-port 29530 examples/role_profile.py [--tokens 8192] [--chunks 2] \
+        [--transport sm|ce|hybrid] [--pusher-ctas 16] [--ce-peers 2] [--side-streams 2] [--probe]
 
 For each linear of the benchmark layer (qkv, gate_up: all-gather+GEMM; o_proj, down:
 GEMM+reduce-scatter; TP=8-local extents) it prints the launch time and, from the library's
@@ -13,11 +14,15 @@ from __future__ import annotations
 
 import argparse
 import os
+import sys
 
 import torch
 import torch.distributed as dist
 
-from . import linear, symm
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from edmir_b200 import linear, symm  # noqa: E402
+from edmir_b200.schedule import Schedule  # noqa: E402
 
 LAYER = (("qkv", "ag_gemm", 8192, 1280), ("gate_up", "ag_gemm", 8192, 7168),
          ("o_proj", "gemm_rs", 1024, 8192), ("down", "gemm_rs", 3584, 8192))
@@ -29,8 +34,13 @@ def main() -> None:
     ap.add_argument("--chunks", type=int, default=2)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--probe", action="store_true")
-    ap.add_argument("--transport", default="sm", choices=("sm", "ce"), help="how all-gather shards travel")
+    ap.add_argument("--transport", default="sm", choices=("sm", "ce", "hybrid"), help="how all-gather shards travel")
+    ap.add_argument("--pusher-ctas", type=int, default=0, help="CTAs that only push the shard (0: push warps in every GEMM CTA)")
+    ap.add_argument("--ce-peers", type=int, default=0, help="hybrid: farthest peers served by copy engines")
+    ap.add_argument("--side-streams", type=int, default=2, help="copy engines: streams the copies are spread over")
     args = ap.parse_args()
+    sched = Schedule(chunks=args.chunks, transport=args.transport, pusher_ctas=args.pusher_ctas,
+                     ce_peers=args.ce_peers, side_streams=args.side_streams)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
@@ -70,8 +80,7 @@ def main() -> None:
         plain_out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         if world > 1:
             if op == "ag_gemm":
-                measure(f"{name} {op} tp{world} chunks{args.chunks} {args.transport}",
-                        lambda: ctx.ag_gemm(a, b, out, chunks=args.chunks, transport=args.transport))
+                measure(f"{name} {op} tp{world} {sched.label()}", lambda: ctx.ag_gemm(a, b, out, schedule=sched))
             else:
                 measure(f"{name} {op} tp{world}", lambda: ctx.gemm_rs(a, b, out))
         measure(f"{name} gemm only", lambda: linear.gemm(full_a, b, plain_out))

@@ -11,6 +11,18 @@
  *
  * The reference has no collective, window or selector code; where an entry point has no
  * reference counterpart its comment says which reference concept it serves instead.
+ *
+ * Threads and devices: the library keeps a little state per device (function attributes,
+ * occupancy, the address of its static scratch, the event that keeps launches sharing its
+ * K-split scratch apart) in tables indexed by the current device and guarded by locks or
+ * atomics, so entry points may be called from several host threads and a process may drive
+ * several GPUs.  A context (edm_comm_t) and the launches on it belong to one thread at a time.
+ * edm_set_timeout_ms / edm_profile_enable are process-wide settings.
+ *
+ * A checking variant of the library (built with -DEDM_DEBUG_BOUNDS, `python -m edmir_b200.build
+ * --checked`) validates every global address the kernels compute against the ranges the launch
+ * may touch and reports a violation as status code 9 (address in the status words) instead of
+ * performing the access; it synchronises around every launch and refuses stream capture.
  */
 #ifndef EDM_B200_H_
 #define EDM_B200_H_
@@ -224,6 +236,43 @@ int edm_gemm_ar_bf16(edm_comm_t* comm, const void* a, int64_t lda, const void* b
 int edm_ag_gemm_bf16(edm_comm_t* comm, const void* x, int64_t ldx, const void* w, int64_t ldw,
                      void* d, int64_t ldd, int64_t M, int64_t N, int64_t K, int32_t chunks,
                      void* stream);
+
+/* ---- expert-parallel mixture-of-experts layer ------------------------------------------
+ * No reference counterpart: the reference names the exchange (comm.all_to_all, EDM-IR/ir/ops.py:35)
+ * and tags nodes with ep_rank (EDM-IR/ir/uop.py:106); a dispatch/combine study is planned
+ * (experiments/deepep-vs-nccl-ep-h100/README.md:19-57).  One call runs, for the `tokens` tokens of
+ * this rank: top-2 routing from the router logits, dispatch of every (token, choice) row to the
+ * rank that holds its expert (stores into symmetric peer windows plus flag words, like the tile
+ * pushes of the fused linears), per-expert down(silu(gate(x)) * up(x)) as two grouped tensor-core
+ * GEMMs, return of the rows and the combination weighted by the softmax of the two selected
+ * logits.  Expert e lives on rank e / (experts / world); every rank of the context makes the same
+ * call.  The context's window must hold edm_moe_window_bytes(); `workspace` (256-byte aligned,
+ * edm_moe_workspace_bytes(), owned by the caller) holds the routing results, the row-block tables
+ * and the intermediate activations.  Like the fused linears the call cannot be stream-captured. */
+typedef struct {
+  int32_t tokens, hidden, ffn, experts; /* T per rank, H, F, E in total (E <= 64, E % world == 0) */
+  const void* x;       /* [T, H] bf16 */
+  int64_t ldx;
+  const float* logits; /* [T, E] fp32 router logits (any bias already added) */
+  int64_t ld_logits;
+  const void* w1;      /* [E/world * 2F, H] bf16: per local expert the gate rows, then the up rows */
+  int64_t ldw1;
+  const void* w2;      /* [E/world * H, F] bf16 */
+  int64_t ldw2;
+  void* out;           /* [T, H] bf16 */
+  int64_t ldo;
+  void* workspace;
+  size_t workspace_bytes;
+} edm_moe_call_t;
+size_t edm_moe_window_bytes(int64_t tokens, int64_t hidden, int64_t experts, int world);
+size_t edm_moe_workspace_bytes(int64_t tokens, int64_t hidden, int64_t ffn, int64_t experts, int world);
+/* Byte offsets inside the workspace of the routing results of the last call: out[0] selected
+ * experts (int32 [T,2]), out[1] their weights (fp32 [T,2]), out[2] the slot of every (token,
+ * choice) among this rank's rows for the same expert (int32 [T,2]). */
+int edm_moe_routing_offsets(int64_t tokens, int64_t hidden, int64_t ffn, int64_t experts, int world, size_t out[3]);
+int edm_moe_forward(edm_comm_t* comm, const edm_moe_call_t* call, void* stream);
+/* n ranks of a group on ONE device: every stage is a single launch over all ranks. */
+int edm_moe_forward_emulated(edm_comm_t* const* comms, const edm_moe_call_t* calls, int n, void* stream);
 
 /* ---- schedule selector -----------------------------------------------------------------
  * Integer restatement of the reference's cost evaluation: a chunked GEMM->collective pipeline

@@ -7,6 +7,7 @@ Every rank builds all ranks' seeded inputs on the CPU, evaluates the oracle loca
 its own device result.  Exit code 0 means every rank passed.  Launched by
 tests/test_multigpu.py when at least two GPUs are visible.
 """
+import dataclasses
 import os
 import sys
 
@@ -18,6 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 from edmir_b200 import linear, symm  # noqa: E402
+from edmir_b200.schedule import Schedule  # noqa: E402
 from oracle import tp_linear as oracle  # noqa: E402
 
 BF16_TOL, FP32_TOL = 1e-2, 1e-5
@@ -45,14 +47,22 @@ def main() -> int:
              ("ag_gemm", 256 * world, 520, 512, torch.bfloat16, 2),
              ("ag_gemm", 64 * world, 256, 128, torch.bfloat16, 1),
              ("ag_gemm_ce", 256 * world, 520, 512, torch.bfloat16, 2),
+             ("ag_gemm_push", 256 * world, 520, 512, torch.bfloat16, 2),
+             ("ag_gemm_push", 64 * world, 256, 136, torch.bfloat16, 1),
+             ("ag_gemm_hybrid", 256 * world, 264, 512, torch.bfloat16, 2),
              ("gemm_ar", 256, 1024, 512, torch.float32, 1)]
     if big:
         cases += [("gemm_rs", 8192, 8192, 1024, torch.bfloat16, 1), ("ag_gemm", 8192, 1280, 8192, torch.bfloat16, 4),
-                  ("ag_gemm_ce", 8192, 1280, 8192, torch.bfloat16, 2)]
+                  ("ag_gemm_ce", 8192, 1280, 8192, torch.bfloat16, 2), ("ag_gemm_push", 8192, 1280, 8192, torch.bfloat16, 4),
+                  ("ag_gemm_hybrid", 8192, 7168, 8192, torch.bfloat16, 2), ("gemm_ar", 1024, 4096, 14336 // world, torch.bfloat16, 1)]
+    schedules = {"": Schedule(transport="sm"), "_ce": Schedule(transport="ce"),
+                 "_push": Schedule(transport="sm", pusher_ctas=16),
+                 "_hybrid": Schedule(transport="hybrid", pusher_ctas=8, ce_peers=max(1, (world - 1) // 2), side_streams=1)}
     for idx, (op, M, N, K, dtype, chunks) in enumerate(cases):
         wscale = 1.0 if dtype == torch.float32 else 0.02
-        transport = "ce" if op.endswith("_ce") else "sm"
-        op = op.replace("_ce", "")
+        suffix = next((k for k in ("_ce", "_push", "_hybrid") if op.endswith(k)), "")
+        op = op[:len(op) - len(suffix)] if suffix else op
+        sched = dataclasses.replace(schedules[suffix], chunks=chunks)
         rows = M // world if op == "ag_gemm" else M
         a_all = [rand((rows, K), 1.0, dtype, 1000 * idx + r) for r in range(world)]
         b_all = [rand((N, K), wscale, dtype, 1000 * idx + 500 + r) for r in range(world)]
@@ -61,12 +71,17 @@ def main() -> int:
         a, b = a_all[rank].to(dev), b_all[rank].to(dev)
         out = None
         for call in range(3):
+            torch.cuda.synchronize()
+            dist.barrier()
+            ctx.poison()           # nobody has copies in flight: a row read before it arrives is a NaN
+            torch.cuda.synchronize()
+            dist.barrier()
             if op == "gemm_rs":
                 out = ctx.gemm_rs(a, b)
             elif op == "gemm_ar":
                 out = ctx.gemm_ar(a, b, out)
             else:
-                out = ctx.ag_gemm(a, b, chunks=chunks, transport=transport)
+                out = ctx.ag_gemm(a, b, schedule=sched)
             torch.cuda.synchronize()
             err = oracle.rel_l2(npf(out), want_all[rank])
             tol = FP32_TOL if dtype == torch.float32 else BF16_TOL

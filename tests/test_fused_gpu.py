@@ -373,7 +373,9 @@ def test_missing_shard_stops_every_role_and_context_survives(group_factory):
     finally:
         linear.set_timeout_ms(2000)
         linear.clear_status()
-    assert st[0] == 7, st[:8]           # a peer's shard chunk never arrived
+    # the role that started waiting first reports: the producer for the shard's chunk flag (7), or
+    # the MMA / epilogue warps that were already waiting for what the producer would have loaded
+    assert st[0] in (1, 3, 7), st[:8]
     assert _lib.load().edm_status_check() == _lib.EDM_OK   # re-armed
     # rows of the own shard were finished before the wait: they are correct; the device works on
     want = oracle.gemm(_np(x), _np(w))
