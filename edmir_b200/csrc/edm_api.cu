@@ -1044,6 +1044,19 @@ int edm_comm_p2p_probe(edm_comm_t* c, int peer, size_t bytes, int mode, void* st
   return EDM_OK;
 }
 
+// Row blocks per band of the tile walk of an all-gather launch, when the caller leaves it open.
+// The walk of a band finishes all its row blocks column by column, so a band reaches as far ahead
+// as it is tall: with weights small enough to stay in L2 whatever the band height (B re-read per
+// band costs nothing then) the band is one chunk of a shard, and tiles start as soon as the first
+// chunk of a shard has landed instead of when its last one has.  0: the kernel's default.
+static int ag_band_for(const edm_tp_call_t& call, const RankParams& P, int cg) {
+  if (P.mode != kAG || P.world <= 1 || call.band_rows > 0 || tuning().band > 0) return 0;
+  if (static_cast<int64_t>(P.N) * P.K * 2 > (32ll << 20)) return 0;
+  const int64_t chunk_rows = (P.M / P.world + P.ag_chunks - 1) / P.ag_chunks;
+  const int64_t blocks = chunk_rows / (kBlockM * cg);
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > 16 ? 16 : blocks));
+}
+
 // Dedicated pusher CTAs of an all-gather launch with `per_rank` CTAs per rank: whole pairs, and at
 // least one unit is left for the tiles.  0 when the kernel pushes nothing.
 static int pusher_ctas_for(const edm_tp_call_t& call, const RankParams& P, int cg, int per_rank, int* out) {
@@ -1080,6 +1093,7 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   lp.profile = g_profile;
   apply_tuning(lp, s);
   if (call->band_rows > 0) lp.band = call->band_rows;
+  else if (const int b = ag_band_for(*call, P, cg)) lp.band = b;
   if (call->band_cols > 0) lp.band_cols = call->band_cols;
   if ((rc = pusher_ctas_for(*call, P, cg, grid, &lp.pusher_ctas))) return rc;
   const bool ce = P.mode == kAG && P.world > 1 && P.ag_ce_lo < P.world;
@@ -1125,6 +1139,7 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   lp.profile = g_profile;
   apply_tuning(lp, s);
   if (calls[0].band_rows > 0) lp.band = calls[0].band_rows;
+  else if (const int b = ag_band_for(calls[0], lp.r[0], cg)) lp.band = b;
   if (calls[0].band_cols > 0) lp.band_cols = calls[0].band_cols;
   if ((rc = pusher_ctas_for(calls[0], lp.r[0], cg, lp.ctas_per_vrank, &lp.pusher_ctas))) return rc;
   // Copies between buffers of ONE device may be carried out by kernels, which cannot start while

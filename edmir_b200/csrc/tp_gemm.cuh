@@ -328,19 +328,23 @@ struct TileWalk {
     Tile t;
     t.valid = true;
     if ((mode == kRS || mode == kAR) && world > 1) {
-      // Round R = i / world: this rank computes tile R of every owner, in the order rank+1,
-      // rank+2, ..., rank.  Pushes therefore leave at a steady rate towards every peer for the
-      // whole launch, and every owner receives the partials of its tile R from all ranks at
-      // about the same time.
+      // Round R = i / world: this rank computes tile R of every owner (rank+1, rank+2, ..., rank,
+      // starting at a rotating position).  Pushes therefore leave at a steady rate towards every
+      // peer for the whole launch, and every owner receives the partials of its tile R from all
+      // ranks at about the same time.
       // The own tiles of the last `defer` rounds are taken out of their rounds and appended.
+      // Inside a round the order of the owners is rotated by the round number.  Units take
+      // positions i, i + units, i + 2 units, ...; with a fixed order and an even number of units a
+      // unit would meet only the owners of one parity class -- at two ranks half of the units
+      // would ship every tile over the link and the other half none.
       const int full = (rounds - defer) * world;        // positions of the undisturbed rounds
       const int thin = defer * (world - 1);             // positions of the rounds without own tile
       int round, d;
-      if (i < full) { round = i / world; d = i - round * world; }
+      if (i < full) { round = i / world; d = (i - round * world + round) % world; }
       else if (i < full + thin) {
         const int j = i - full;
         round = rounds - defer + j / (world - 1);
-        d = j - (j / (world - 1)) * (world - 1);        // 0 .. world-2: never this rank
+        d = (j - (j / (world - 1)) * (world - 1) + round) % (world - 1);  // 0 .. world-2: never this rank
       } else { round = rounds - defer + (i - full - thin); d = world - 1; }
       t.owner = (rank + 1 + d) % world;
       t.owned_idx = round;

@@ -64,8 +64,15 @@ def test_reduce_walk_sends_to_every_peer_each_round_and_ends_on_own_tiles(native
             defer = min(rounds, units)
             head = walk[:(rounds - defer) * world]
             for r in range(rounds - defer):
+                # every round reaches every owner once, starting at a position that rotates with the round
                 assert [o for _, _, o, _ in head[r * world:(r + 1) * world]] == \
-                    [(rank + 1 + d) % world for d in range(world)]
+                    [(rank + 1 + (d + r) % world) % world for d in range(world)]
+            # a unit (every units-th position) therefore alternates between owners: with a fixed
+            # order and an even unit count it would only ever meet one parity class of them
+            for u in (0, 1):
+                mine = [o for _, _, o, _ in head[u::units]]
+                if len(mine) >= 4:
+                    assert {(o - rank) % 2 for o in mine} == {0, 1}, (op, rank, u, mine)
             tail = walk[-defer:]
             assert all(o == rank for _, _, o, _ in tail)
             middle = walk[(rounds - defer) * world:len(walk) - defer]
