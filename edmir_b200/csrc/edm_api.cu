@@ -1024,12 +1024,12 @@ int edm_tail_split(int64_t tiles, int units, int64_t k_blocks, int32_t out[3]) {
 }
 
 int edm_comm_p2p_probe(edm_comm_t* c, int peer, size_t bytes, int mode, void* stream) {
-  if (!c || peer < 0 || peer >= c->world || !c->base[peer] || (mode != 0 && mode != 1)) return EDM_ERR_BAD_ARG;
-  if (bytes == 0 || bytes % 8192 || bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
+  if (!c || peer < 0 || peer >= c->world || !c->base[peer] || mode < 0 || mode > 3) return EDM_ERR_BAD_ARG;
+  if (bytes == 0 || bytes % 32768 || bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
   static std::atomic<bool> configured[kMaxDevices] = {};
-  const int smem = 8 * 2 * 8192 + 128;
+  const int smem = 6 * 2 * 16384 + 128;  // the largest of the modes' staging
   const int dev = current_device();
   if (dev < 0) return EDM_ERR_UNSUPPORTED;
   if (!configured[dev].load(std::memory_order_acquire)) {

@@ -1604,13 +1604,16 @@ __global__ void split_tf32_kernel(const float* __restrict__ x, float* __restrict
 }
 
 // ------------------------------------------------------------------ link probe
-// Copies `bytes` from local memory into a peer's window, with the two store mechanisms the
-// fused kernel uses, so the host can measure what the link sustains (calibration of the
-// schedule selector's transfer term).  mode 0: 16-byte loads and stores from every thread;
-// mode 1: every warp stages 8 KiB in shared memory and ships it with one bulk copy.
+// Copies `bytes` from local memory into a peer's window, with the store mechanisms the fused
+// kernels use, so the host can measure what the link sustains (calibration of the schedule
+// selector's transfer term).  mode 0: 16-byte loads and stores from every thread; mode 1: every
+// warp stages 8 KiB in shared memory and ships it with one bulk copy; modes 2 and 3: the pusher
+// CTAs' mechanism -- bulk load into shared memory, bulk store from there, one lane per warp --
+// with 16 KiB (6 warps x 2 buffers) and 32 KiB (3 warps x 2 buffers) per copy.
 __global__ void __launch_bounds__(256, 1)
 p2p_probe_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t bytes, int mode) {
   extern __shared__ uint8_t probe_smem[];
+  __shared__ uint64_t probe_bars[12];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (mode == 0) {
     const size_t nvec = bytes / 16;
@@ -1629,7 +1632,7 @@ p2p_probe_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t by
         if (v < nvec) st_global_v4(dst + v * 16, buf[u]);
       }
     }
-  } else {
+  } else if (mode == 1) {
     constexpr uint32_t kChunk = 8192;
     const uint32_t base = (smem_u32(probe_smem) + 127u) & ~127u;
     const uint32_t buf0 = base + warp * 2 * kChunk;
@@ -1652,6 +1655,43 @@ p2p_probe_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t by
       }
     }
     if (lane == 0) bulk_wait_all();
+  } else {
+    const uint32_t chunk = mode == 2 ? 16384u : 32768u;
+    const int warps = mode == 2 ? 6 : 3;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < 12; ++i) mbar_init(smem_u32(&probe_bars[i]), 1);
+      mbar_fence_init();
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    if (warp >= warps || lane != 0) return;
+    const uint32_t base = (smem_u32(probe_smem) + 127u) & ~127u;
+    const uint32_t buf0 = base + warp * 2 * chunk;
+    const uint32_t bar0 = smem_u32(&probe_bars[warp * 2]);
+    const size_t nchunks = bytes / chunk;
+    const size_t gw = static_cast<size_t>(blockIdx.x) * warps + warp, tw = static_cast<size_t>(gridDim.x) * warps;
+    uint32_t n = 0;
+    size_t next = gw;
+    if (next < nchunks) {  // one load ahead of the stores
+      mbar_arrive_expect_tx(bar0, chunk);
+      bulk_load(buf0, src + next * chunk, chunk, bar0);
+    }
+    for (size_t c = gw; c < nchunks; c += tw, ++n) {
+      const uint32_t b = n & 1u;
+      uint32_t spins = 0;
+      while (!mbar_try_wait(bar0 + 8 * b, (n >> 1) & 1u))
+        if (++spins > (1u << 24)) return;  // bounded: a load that never lands ends the probe
+      bulk_store(dst + c * chunk, buf0 + b * chunk, chunk);
+      bulk_commit();
+      const size_t nx = c + tw;
+      if (nx < nchunks) {
+        // the other buffer was read by the store before this one
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        mbar_arrive_expect_tx(bar0 + 8 * (b ^ 1u), chunk);
+        bulk_load(buf0 + (b ^ 1u) * chunk, src + nx * chunk, chunk, bar0 + 8 * (b ^ 1u));
+      }
+    }
+    bulk_wait_all();
   }
 }
 

@@ -346,6 +346,17 @@ def lower(spec: TPLinearSpec, ctx, schedule: Schedule) -> Callable:
     return unfused
 
 
+def lower_emulated(spec: TPLinearSpec, group, schedule: Schedule) -> Callable:
+    """The same lowering for a ``symm.EmulatedGroup`` (all ranks of the group on one device, one
+    cooperative launch): returns ``fn(a_list, b_list, out_list) -> out_list``.  Only fused
+    schedules can be emulated (the unfused one needs a process group)."""
+    if not schedule.fused:
+        raise ValueError("the unfused schedule runs a torch.distributed collective: it cannot be emulated on one device")
+    if group.world != spec.world:
+        raise ValueError("the group's size differs from the spec's")
+    return lambda a_list, b_list, out_list: group.run(spec.op, a_list, b_list, out_list, schedule=schedule)
+
+
 def nvtx_name(namespace: str, name: str, iteration: int | None = None) -> str:
     """``edm.<ns>:<name>[.iter<N>]`` -- the range-name grammar the reference's profiler import
     parses (EDM-IR/ir/nsys_export.py:17, :74-88)."""

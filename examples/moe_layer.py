@@ -95,10 +95,10 @@ def main() -> None:
         if world > 1:
             dist.broadcast(w1_e, owner)
             dist.broadcast(w2_e, owner)
-        for k in range(2):
-            hit = sel[:, k] == e
-            if hit.any():
-                want[hit] += wts[hit, k:k + 1] * oracle.expert_ffn(xs[hit], w1_e.float().cpu().numpy(), w2_e.float().cpu().numpy())
+        hit = (sel == e).any(axis=1)          # an expert is selected at most once per token
+        if hit.any():
+            weight = np.where(sel[hit] == e, wts[hit], 0.0).sum(axis=1, keepdims=True)
+            want[hit] += weight * oracle.expert_ffn(xs[hit], w1_e.float().cpu().numpy(), w2_e.float().cpu().numpy())
     err = torch.tensor([tpo.rel_l2(out[pick.to(dev)].float().cpu().numpy(), want)], device=dev, dtype=torch.float64)
     same_idx = torch.tensor([float(np.array_equal(idx[pick.to(dev)].cpu().numpy(), sel))], device=dev)
     if world > 1:

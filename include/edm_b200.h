@@ -155,9 +155,10 @@ int edm_comm_heap_reset(edm_comm_t* comm);
  * its sender wrote it shows up in the output instead of silently re-using the previous call's
  * data.  Every rank must have finished its previous launch (no copies in flight). */
 int edm_comm_poison(edm_comm_t* comm, int byte_value, void* stream);
-/* Link probe for calibration: copies `bytes` (a multiple of 8192, at most half the window) from
+/* Link probe for calibration: copies `bytes` (a multiple of 32768, at most half the window) from
  * this rank's window into `peer`'s with mode 0 = 16-byte stores from every thread, mode 1 =
- * 8 KiB bulk copies staged through shared memory.  The caller times it with CUDA events; the
+ * 8 KiB bulk copies staged through shared memory by all lanes, modes 2 / 3 = the pusher CTAs'
+ * bulk-load-then-bulk-store pipeline with 16 / 32 KiB per copy.  The caller times it with CUDA events; the
  * figures feed the selector's transfer term ("calibrated from ... P2P tests",
  * paper/mlsys-2027/model.md:111).  Both ranks of a pair may probe each other at once. */
 int edm_comm_p2p_probe(edm_comm_t* comm, int peer, size_t bytes, int mode, void* stream);
