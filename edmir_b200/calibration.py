@@ -28,7 +28,8 @@ class Calibration:
       256x256 tile and per tile (fill, drain, epilogue hand-over); they set the cost of short-K tiles.
     ``link_gbs``: what one GPU pushes into its peers' windows per direction with every SM storing.
     ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
-    ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams.
+    ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams when the
+      shard goes to several peers (measured at 8 ranks); ``ce_gbs_one_peer``: to a single peer (2 ranks).
     ``sm_push_slowdown``: factor on the GEMM when warps inside every GEMM CTA push the shard.
     ``publish_ns``: latency from "data landed" to "flag visible" (one system-scope fence batch).
     ``launch_ns``: start-up and tear-down of one fused launch; ``ce_launch_ns``: what the stream
@@ -47,6 +48,7 @@ class Calibration:
     link_gbs: float = 650.0
     pusher_cta_gbs: float = 45.0
     ce_gbs: tuple = (290.0, 470.0, 470.0, 470.0)
+    ce_gbs_one_peer: float = 740.0
     ag_link_gbs: float = 470.0
     sm_push_slowdown: float = 1.17
     nccl_gbs: float = 380.0
@@ -71,7 +73,9 @@ class Calibration:
         return {"nvlink_gbs_per_dir": self.link_gbs, "bf16_tflops": self.gemm_tflops,
                 "flag_publish_ns": self.publish_ns, **self.extra}
 
-    def ce_rate(self, side_streams: int) -> float:
+    def ce_rate(self, side_streams: int, peers: int = 7) -> float:
+        if peers <= 1:
+            return float(self.ce_gbs_one_peer)
         n = min(max(side_streams, 1), len(self.ce_gbs))
         return float(self.ce_gbs[n - 1])
 

@@ -183,7 +183,7 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
             total = int(total * calib.sm_push_slowdown)  # push warps share the GEMM CTAs' memory pipes
         push_rate = min(calib.link_gbs, pushers * calib.pusher_cta_gbs) if pushers else calib.link_gbs
         n_streams = min(max(sched.side_streams, 1), max(W - ce_lo, 1)) if uses_ce else 0
-        ce_rate = calib.ce_rate(n_streams) if uses_ce else 0.0
+        ce_rate = calib.ce_rate(n_streams, W - ce_lo) if uses_ce else 0.0
         if pushes and uses_ce and push_rate + ce_rate > calib.link_gbs:  # both share the link
             scale = calib.link_gbs / (push_rate + ce_rate)
             push_rate, ce_rate = push_rate * scale, ce_rate * scale

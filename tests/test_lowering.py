@@ -135,3 +135,16 @@ def test_measured_graph_reports_exposed_communication():
     assert lowering.launch_range_name(one) == "edm.compute:gemm"
     single = lowering.measured_graph(one, Schedule(), 5.0, 5.0)
     assert analyze_exposure(single).total_comm_us == 0.0
+
+
+def test_example_scripts_compile():
+    # the examples need GPUs (most of them several) to run; here they only have to parse and import-check
+    import glob
+    import os
+    import py_compile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    scripts = sorted(glob.glob(os.path.join(root, "examples", "*.py")))
+    assert len(scripts) >= 6
+    for path in scripts:
+        py_compile.compile(path, doraise=True)
