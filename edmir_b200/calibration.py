@@ -26,7 +26,13 @@ class Calibration:
     ``gemm_tflops``: bf16 rate of the GEMM kernel on all ``gemm_units`` CTA pairs at large shapes.
     ``tile_ns_per_kblock`` / ``tile_fixed_ns``: time a CTA pair spends per 64-element K block of a
       256x256 tile and per tile (fill, drain, epilogue hand-over); they set the cost of short-K tiles.
-    ``link_gbs``: what one GPU pushes into its peers' windows per direction with every SM storing.
+    ``link_gbs``: what one GPU pushes per direction to one peer at a time (the link probe; the
+      pusher CTAs of an all-gather, which serve their peers one after the other, reach it).
+    ``fabric_gbs``: what it pushes per direction when every rank of an 8-rank group sends to all its
+      peers at once (tile pushes of the reduce-scatter; the library collectives land there too).
+    ``ce_op_ns``: what every further copy + flag write costs a copy-engine stream;
+    ``push_chunk_ns``: what a chunk boundary costs the pusher warps (their pipelines drain);
+    ``push_publish_ns``: latency from "all pusher warps have counted a chunk" to "flag visible".
     ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
     ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams when the
       shard goes to several peers (measured at 8 ranks); ``ce_gbs_one_peer``: to a single peer (2 ranks).
@@ -46,9 +52,13 @@ class Calibration:
     tile_ns_per_kblock: int = 100
     tile_fixed_ns: int = 1_200
     link_gbs: float = 650.0
-    pusher_cta_gbs: float = 45.0
-    ce_gbs: tuple = (290.0, 470.0, 470.0, 470.0)
+    fabric_gbs: float = 520.0
+    pusher_cta_gbs: float = 48.0
+    ce_gbs: tuple = (315.0, 515.0, 515.0, 515.0)
     ce_gbs_one_peer: float = 740.0
+    ce_op_ns: int = 5_000
+    push_chunk_ns: int = 1_500
+    push_publish_ns: int = 5_000
     ag_link_gbs: float = 470.0
     sm_push_slowdown: float = 1.17
     nccl_gbs: float = 380.0
@@ -73,6 +83,14 @@ class Calibration:
         return {"nvlink_gbs_per_dir": self.link_gbs, "bf16_tflops": self.gemm_tflops,
                 "flag_publish_ns": self.publish_ns, **self.extra}
 
+    def all_to_all_rate(self, world: int) -> float:
+        """Per-direction rate when every rank pushes to all peers at once: the pair rate at two ranks,
+        the fabric rate from eight on, linear in between."""
+        if world <= 2:
+            return float(self.link_gbs)
+        f = min(world - 2, 6) / 6.0
+        return float(self.link_gbs + f * (self.fabric_gbs - self.link_gbs))
+
     def ce_rate(self, side_streams: int, peers: int = 7) -> float:
         if peers <= 1:
             return float(self.ce_gbs_one_peer)
@@ -93,14 +111,35 @@ def wire_bytes(op: str, M: int, N: int, K: int, world: int, elem_bytes: int = 2)
     raise ValueError(f"unknown op {op}")
 
 
+def tile_ns(K: int, calib: Calibration, elem_bytes: int = 2) -> int:
+    """Time a CTA pair needs for one 256x256 tile: its K blocks plus a fixed part."""
+    k_blocks = -(-K * elem_bytes // 128)
+    return k_blocks * calib.tile_ns_per_kblock + calib.tile_fixed_ns
+
+
+def last_wave(tiles: int, units: int, k_blocks: int) -> float:
+    """What the incomplete last wave of ``tiles`` on ``units`` CTA pairs costs, in tile times: its
+    tiles are cut along K into 2, 4 or 8 pieces when that many free pairs exist (the kernel's rule),
+    plus the exchange of partial sums; a whole tile time otherwise."""
+    rest = tiles % units
+    if rest == 0:
+        return 0.0
+    parts = 1
+    if k_blocks >= 32:
+        parts = min(units // rest, k_blocks // 4, 8)
+        while parts & (parts - 1):
+            parts &= parts - 1
+    return 1.0 if parts < 2 else 1.0 / parts + 0.15
+
+
 def gemm_ns(M: int, N: int, K: int, calib: Calibration, units: int | None = None, elem_bytes: int = 2) -> int:
-    """Time of the GEMM alone on ``units`` CTA pairs: whole waves of 256x256 tiles, each costing
-    its K blocks plus a fixed part, but never less than the flops at the calibrated rate."""
+    """Time of the GEMM alone on ``units`` CTA pairs: whole waves of 256x256 tiles plus the last
+    one (see ``last_wave``), but never less than the flops at the calibrated rate."""
     units = calib.gemm_units if units is None else max(units, 1)
     tiles = -(-M // 256) * -(-N // 256)
     k_blocks = -(-K * elem_bytes // 128)
-    waves = -(-tiles // units)
-    by_tiles = waves * (k_blocks * calib.tile_ns_per_kblock + calib.tile_fixed_ns)
+    waves = tiles // units + last_wave(tiles, units, k_blocks)
+    by_tiles = int(waves * tile_ns(K, calib, elem_bytes))
     by_rate = int(round(2 * M * N * K / (calib.gemm_tflops * 1e3) * calib.gemm_units / units))  # TFLOP/s = 1e3 flop/ns
     return max(by_tiles, by_rate)
 

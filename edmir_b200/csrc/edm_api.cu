@@ -636,7 +636,7 @@ int plan_layout(const edm_comm* c, const edm_tp_call_t& call, int out_bytes, int
     L.window_need = static_cast<size_t>(call.M) * call.K * elem_bytes;
     L.gather_off = 0;
     L.flag_words = static_cast<uint32_t>(W) * call.chunks;
-    if (static_cast<size_t>(W) * call.chunks * 4 > c->counter_bytes) return EDM_ERR_CAPACITY;
+    if (static_cast<size_t>(W) * call.chunks * 4 > c->counter_bytes / 2) return EDM_ERR_CAPACITY;
   } else {
     return EDM_ERR_BAD_ARG;
   }
@@ -689,7 +689,9 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     P.win[p] = c->base[p] + c->off_window() + par * (c->window_bytes / 2);
     P.gather[p] = P.win[p];
   }
-  P.counters = reinterpret_cast<uint32_t*>(c->base[c->rank] + c->off_counters());
+  // two banks of arrival counters, by epoch parity: a call uses one and clears the other
+  P.counters = reinterpret_cast<uint32_t*>(c->base[c->rank] + c->off_counters() + par * (c->counter_bytes / 2));
+  P.counters_next = reinterpret_cast<uint32_t*>(c->base[c->rank] + c->off_counters() + (par ^ 1u) * (c->counter_bytes / 2));
   P.epoch = epoch;
   P.max_owned = L.max_owned;
   P.partial_flag_off = L.partial_off;

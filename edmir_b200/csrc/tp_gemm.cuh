@@ -70,6 +70,7 @@ enum Status : uint32_t {
   kTimeoutGatherFlag = 7,    // AG: a peer's shard chunk never arrived
   kTimeoutTailFlag = 8,      // split last wave: another CTA's partial sum never arrived
   kBoundsFault = 9,          // checking build only: an address outside every range the launch may touch
+  kTimeoutPushCount = 10,    // AG with pusher CTAs: this rank's own pushers never finished a chunk
 };
 
 __device__ uint32_t g_status[16];
@@ -111,7 +112,8 @@ struct alignas(64) RankParams {
   int64_t ld_out;          // elements
   const void* x_local;     // AG: this rank's shard [M/world,K]
   int64_t ld_x;            // elements
-  uint32_t* counters;      // AG: local arrival counters [world*ag_chunks]
+  uint32_t* counters;      // AG: local arrival counters [world*ag_chunks], bank of this call's epoch parity
+  uint32_t* counters_next; // AG: the other bank; the publisher zeroes it for the next call
   float* scratch;          // split-fp32: running fp32 sums, one kBlockM x kBlockN tile per CTA
   int32_t seg_kblocks;     // split-fp32: K blocks accumulated in TMEM before folding into scratch (0 = all)
   int32_t ag_external;     // AG: shards and chunk flags are delivered by copy engines, not by this kernel
@@ -882,11 +884,13 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   // One lane of each of kPusherWarps warps moves 8 KiB segments of the shard: bulk load from local
   // memory into one of its kPushDepth staging buffers, bulk store from there into the peer's gather
   // buffer.  Loads run kPushDepth - 1 segments ahead of the stores.  Segments are dealt round-robin
-  // over all pusher warps of the rank; a warp posts one note per (peer, chunk) -- also when it
-  // moved nothing of it -- once its copies of that chunk have been written, and the signaller that
-  // counts the last note raises the chunk's flag at the peer.  Waiting for "written" right after
-  // the last copy of a chunk would drain the warp's pipeline, so the note goes out kPushDepth
-  // segments later, when the bulk-group count alone proves the chunk's copies complete.
+  // over all pusher warps of the rank; a warp counts every (peer, chunk) -- also when it moved
+  // nothing of it -- once its copies of that chunk have been written: one relaxed add on the
+  // chunk's arrival counter and no fence (a system-scope fence on an SM with remote writes queued
+  // costs tens of microseconds; the completed bulk groups have performed their writes).  The flag
+  // at the peer is raised by the publisher below, on an SM that pushes nothing.  Waiting for
+  // "written" right after the last copy of a chunk would drain the warp's pipeline, so the count
+  // goes out kPushDepth segments later, when the bulk-group count alone proves the copies complete.
   auto pusher_role = [&](int w) {
     if (lane != 0) return;
     ProfTimer push_total(prof && w == 0);
@@ -933,13 +937,17 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
         u.s += T;
         return 0;
       }
-      note = make_note(kNoteChunk, (static_cast<uint64_t>(peer) << 24) | static_cast<uint64_t>(u.c));
+      note = static_cast<uint64_t>(peer * P.ag_chunks + u.c);  // index of the chunk's arrival counter
       u.rot = (u.rot + u.nseg) % T;
       if (++u.c == P.ag_chunks) { u.c = 0; ++u.d; }
       if (u.d < d_hi) open_chunk(u);
       return 1;
     };
 
+    auto count_chunk = [&](uint64_t idx) {
+      uint32_t* ctr = P.counters + idx;
+      if (EDM_ADDR_OK(ctr, 4, 20u)) atomicAdd(ctr, 1u);
+    };
     Cursor lc{first_d, 0, 0, 0, 0, 0, 0};
     if (first_d < d_hi) open_chunk(lc);
     Cursor sc = lc;
@@ -968,7 +976,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       if (k == 1) {
         if (pending) {
           bulk_wait_pending<0>();
-          mailbox_post(&mbox[w], pending_note, timeout_ns);
+          count_chunk(pending_note);
         }
         pending = true; pending_note = note; since = 0;
         continue;
@@ -986,13 +994,51 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
       issue_load();
       if (pending && ++since >= static_cast<uint32_t>(kPushDepth)) {
         bulk_wait_pending<kPushDepth>();  // everything older than the last kPushDepth copies is written
-        mailbox_post(&mbox[w], pending_note, timeout_ns);
+        count_chunk(pending_note);
         pending = false;
       }
     }
     bulk_wait_pending<0>();
-    if (pending && !aborted()) mailbox_post(&mbox[w], pending_note, timeout_ns);
+    if (pending && !aborted()) count_chunk(pending_note);
     push_total.stop(kProfPushTotal);
+  };
+
+  // ------------------------------------------------------------------ publisher (pusher CTAs)
+  // One lane of the first tile CTA of the rank -- an SM that issues no remote stores, so its
+  // system-scope fence is cheap -- walks the (peer, chunk) pairs in the order the pushers finish
+  // them, waits until all pusher warps have counted a chunk, and raises the chunk's flag at the
+  // peer.  A counter is re-armed as soon as it has been consumed; the counters of the other bank
+  // (epoch parity) are zeroed as well, so that a launch that gave up part-way does not leave stale
+  // counts to the call after the next.
+  auto publisher_role = [&]() {
+    if (lane != 0) return;
+    const int first_d = P.ag_local_direct ? 1 : 0;
+    const int d_hi = min(P.world, P.ag_ce_lo);
+    const uint32_t target = static_cast<uint32_t>(pusher_ctas * kPusherWarps);
+    for (int i = 0; i < P.world * P.ag_chunks; ++i)
+      if (EDM_ADDR_OK(P.counters_next + i, 4, 21u)) P.counters_next[i] = 0u;
+    for (int d = first_d; d < d_hi; ++d) {
+      const int peer = (P.rank - d + P.world) % P.world;
+      for (int c = 0; c < P.ag_chunks; ++c) {
+        const uint32_t* ctr = P.counters + peer * P.ag_chunks + c;
+        if (!EDM_ADDR_OK(ctr, 4, 22u)) return;
+        uint64_t t0 = 0;
+        uint32_t spins = 0;
+        while (ld_acquire_gpu(ctr) < target) {
+          if ((spins++ & 31u) == 0u) {
+            if (aborted()) return;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > timeout_ns) { report(kTimeoutPushCount, (peer << 16) | c, target, ld_acquire_gpu(ctr)); return; }
+          }
+          __nanosleep(100);
+        }
+        *reinterpret_cast<volatile uint32_t*>(P.counters + peer * P.ag_chunks + c) = 0u;  // re-armed for a later call
+        fence_acq_rel_sys();
+        uint32_t* flag = P.flags[peer] + P.gather_flag_off + P.rank * P.ag_chunks + c;
+        if (EDM_ADDR_OK(flag, 4, 23u)) st_relaxed_sys(flag, P.epoch);
+      }
+    }
   };
 
   // ------------------------------------------------------------------ signaller
@@ -1053,16 +1099,7 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
 
   if (is_pusher) {
     // ============================ pusher CTA ============================
-    if (warp < kPusherWarps) {
-      pusher_role(warp);
-      if (lane == 0) mailbox_close(&mbox[warp]);
-    } else if (warp == 8) {
-      signaller_role();
-    } else if (lane == 0) {
-      // mailboxes nobody posts to: warps 6, 7 close theirs, warp 9 closes the last one
-      if (warp < 8) mailbox_close(&mbox[warp]);
-      else if (warp == 9) mailbox_close(&mbox[8]);
-    }
+    if (warp < kPusherWarps) pusher_role(warp);
   } else if (warp == 0) {
     // ============================ TMA producer ============================
     if (lane == 0) {
@@ -1562,8 +1599,9 @@ tp_gemm_kernel(const __grid_constant__ LaunchParams lp) {
   }
 
   else if (warp == 8) {
-    // ============================ signaller ============================
-    signaller_role();
+    // ============================ signaller / publisher ============================
+    if (pusher_ctas > 0) { if (cta_in_rank == 0) publisher_role(); }
+    else signaller_role();
   } else {
     // ============================ extra reducers / push warps (warps 9-11) ============================
     if (fused_reduce) reduce_units(&mbox[6 + (warp - 9)], false);

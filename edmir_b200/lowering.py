@@ -24,7 +24,7 @@ from functools import lru_cache
 from typing import Callable, Sequence
 
 from . import _lib
-from .calibration import Calibration, gemm_ns, wire_bytes
+from .calibration import Calibration, gemm_ns, tile_ns, wire_bytes
 from .ir import EDMBuilder, EDMGraph, MovementDesc, TensorDesc
 from .ir import ops as irops
 from .schedule import Schedule
@@ -190,6 +190,9 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
         shard = wire // (W - 1)
         setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP,
                          calib.launch_ns + skew + (calib.ce_launch_ns if uses_ce else 0), stream="compute")
+        # a tile cannot finish sooner than one tile time after its rows have landed (half of it plus
+        # the exchange where the last wave is cut along K)
+        floor = int(tile_ns(spec.K, calib) * (0.65 if spec.K * 2 // 128 >= 32 else 1.0))
         # transfers: one chain per carrier, shards in the order their consumers need them
         last = {"push": setup}
         for s in range(n_streams):
@@ -200,14 +203,18 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
                 stream, rate, backend = "push", push_rate, "nvlink-p2p"
             else:
                 stream, rate, backend = f"ce{d % n_streams}", ce_rate / n_streams, "copy-engine"
+            pushed = d < ce_lo
+            per_chunk = (calib.push_chunk_ns if pushers else 0) if pushed else calib.ce_op_ns
+            publish = (calib.push_publish_ns if pushers else calib.publish_ns) if pushed else 0
             for k in range(c):
                 nbytes = shard // c + (1 if k < shard % c else 0)
-                node = plan.add("comm", f"all_gather.s{d}.c{k}", comm_op, int(nbytes / rate), stream=stream,
+                node = plan.add("comm", f"all_gather.s{d}.c{k}", comm_op, int(nbytes / rate) + per_chunk, stream=stream,
                                 after=last[stream], movement=move(nbytes, backend),
                                 attrs={**attrs, "chunk": k, "shard": d})
                 last[stream] = node
-                # the chunk's flag becomes visible one publication later (not link time)
-                ready[(d, k)] = plan.add("other", f"flag.s{d}.c{k}", irops.EVENT_RECORD, calib.publish_ns,
+                # the chunk's flag becomes visible one publication later (not link time); a copy
+                # engine's flag write is part of its stream operation
+                ready[(d, k)] = plan.add("other", f"flag.s{d}.c{k}", irops.EVENT_RECORD, publish,
                                          deps=(node,), stream=stream + ".flags")
         prev = setup
         for j in range(W):
@@ -216,6 +223,9 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
                 deps = (ready[(j, k)],) if j > 0 else ()
                 prev = plan.add("compute", f"gemm.s{j}.c{k}", irops.COMPUTE_GEMM, share, deps=deps, stream="compute",
                                 after=prev, attrs={**attrs, "chunk": k, "shard": j})
+                if j > 0 and share < floor:
+                    plan.add("compute", f"tile.s{j}.c{k}", irops.COMPUTE_GEMM, floor, deps=deps, stream=f"tiles.s{j}",
+                             attrs={**attrs, "chunk": k, "shard": j})
         return plan.build(common)
 
     # GEMM + reduce-scatter / all-reduce: tiles are pushed as they finish; modelled as G groups of
@@ -231,7 +241,7 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
         g_prev = plan.add("compute", f"gemm.{i}", irops.COMPUTE_GEMM, total // G + (1 if i < total % G else 0),
                           stream="compute", after=g_prev, attrs={**attrs, "chunk": i})
         nbytes = push_bytes // G + (1 if i < push_bytes % G else 0)
-        m_prev = plan.add("comm", f"{spec.op}.{i}", comm_op, int(nbytes / calib.link_gbs), deps=(g_prev,), stream="push",
+        m_prev = plan.add("comm", f"{spec.op}.{i}", comm_op, int(nbytes / calib.all_to_all_rate(W)), deps=(g_prev,), stream="push",
                           after=m_prev, movement=move(nbytes, "nvlink-p2p"), attrs={**attrs, "chunk": i})
     flag = plan.add("other", "flags", irops.EVENT_RECORD, calib.publish_ns, deps=(m_prev,), stream="push.flags")
     own_bytes = (spec.M // W if spec.op == "gemm_rs" else -(-spec.M // W)) * spec.N * 2
@@ -240,7 +250,7 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
     if spec.op == "gemm_ar":
         # the owner stores the reduced tiles into every rank's output: the second half of the wire bytes
         tail = wire // 2 // G
-        plan.add("comm", "gemm_ar.result", comm_op, int(tail / calib.link_gbs) + calib.publish_ns, deps=(red,),
+        plan.add("comm", "gemm_ar.result", comm_op, int(tail / calib.all_to_all_rate(W)) + calib.publish_ns, deps=(red,),
                  stream="push", movement=move(tail, "nvlink-p2p"), attrs=dict(attrs))
     return plan.build(common)
 
