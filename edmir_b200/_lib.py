@@ -29,6 +29,7 @@ EDM_OP_AG_GEMM = 3
 EDM_TRANSPORT_SM = 0
 EDM_TRANSPORT_COPY_ENGINE = 1
 EDM_TRANSPORT_HYBRID = 2
+EDM_TRANSPORT_COPY_ENGINE_STRIPED = 3
 
 EDM_MAX_RANKS = 8
 EDM_IPC_HANDLE_BYTES = 64
@@ -55,7 +56,7 @@ class TpCall(C.Structure):
         ("chunks", C.c_int32), ("transport", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("pusher_ctas", C.c_int32), ("ce_peers", C.c_int32), ("side_streams", C.c_int32),
-        ("band_rows", C.c_int32), ("band_cols", C.c_int32), ("reserved", C.c_int32),
+        ("band_rows", C.c_int32), ("band_cols", C.c_int32), ("one_shot", C.c_int32),
     ]
 
 

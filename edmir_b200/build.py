@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libedm_b200.so")
 SOURCES = ["edm_api.cu", "selector.cpp"]
-HEADERS = ["ptx.cuh", "tp_gemm.cuh", os.path.join("..", "..", "include", "edm_b200.h")]
+HEADERS = ["ptx.cuh", "tp_gemm.cuh", "moe.cuh", "ar_oneshot.cuh", os.path.join("..", "..", "include", "edm_b200.h")]
 
 
 def _nvcc() -> str:
@@ -48,10 +48,11 @@ def build(force: bool = False, verbose: bool = False, out: str = LIB_PATH, defin
     """Compile the library if it is missing or older than its sources; return its path."""
     if out == LIB_PATH and not force and not _stale():
         return LIB_PATH
+    tmp = f"{out}.{os.getpid()}.tmp"   # a reader never sees a half-written library
     cmd = [
         _nvcc(), "-shared", "-Xcompiler", "-fPIC", "-std=c++17", "-O3", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
-        "-o", out,
+        "-o", tmp,
     ] + [f"-D{d}" for d in defines] + [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -60,7 +61,10 @@ def build(force: bool = False, verbose: bool = False, out: str = LIB_PATH, defin
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError(f"nvcc failed building {os.path.basename(out)}")
+    os.replace(tmp, out)
     return out
 
 

@@ -32,6 +32,8 @@ class Calibration:
       peers at once (tile pushes of the reduce-scatter; the library collectives land there too).
     ``ce_op_ns``: what every further copy + flag write costs a copy-engine stream;
     ``push_chunk_ns``: what a chunk boundary costs the pusher warps (their pipelines drain);
+    ``sm_chunk_ns``: what it costs push warps inside the GEMM CTAs (a fence on a busy SM per flag);
+    ``one_shot_sync_ns``: one-shot all-reduce -- second launch, fence, flag flight, first remote load;
     ``push_publish_ns``: latency from "all pusher warps have counted a chunk" to "flag visible".
     ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
     ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams when the
@@ -58,6 +60,8 @@ class Calibration:
     ce_gbs_one_peer: float = 740.0
     ce_op_ns: int = 5_000
     push_chunk_ns: int = 1_500
+    sm_chunk_ns: int = 4_500
+    one_shot_sync_ns: int = 8_000
     push_publish_ns: int = 5_000
     ag_link_gbs: float = 470.0
     sm_push_slowdown: float = 1.17

@@ -12,6 +12,7 @@
 #include "../../include/edm_b200.h"
 #include "tp_gemm.cuh"
 #include "moe.cuh"
+#include "ar_oneshot.cuh"
 
 using namespace edm;
 
@@ -710,7 +711,7 @@ int build_rank_params(edm_comm* c, const edm_tp_call_t& call, int cg, RankParams
     // which peers (rank-d, d = 1 .. W-1; d = 0 is the own shard when it is not read in place) get
     // the shard from copy engines: all, none, or the ce_peers farthest ones
     const int first_d = P.ag_local_direct ? 1 : 0;
-    if (call.transport == EDM_TRANSPORT_COPY_ENGINE) {
+    if (call.transport == EDM_TRANSPORT_COPY_ENGINE || call.transport == EDM_TRANSPORT_COPY_ENGINE_STRIPED) {
       P.ag_ce_lo = first_d;
     } else if (call.transport == EDM_TRANSPORT_HYBRID) {
       if (call.ce_peers < 0 || call.ce_peers > W - 1) return EDM_ERR_BAD_ARG;
@@ -765,7 +766,7 @@ int ag_copy_engine_mark(edm_comm* c, cudaStream_t stream) {
   EDM_CUDA(cudaEventRecord(c->ev_in, stream));
   return EDM_OK;
 }
-int ag_copy_engine_issue(edm_comm* c, const RankParams& P, int side_streams, cudaStream_t stream) {
+int ag_copy_engine_issue(edm_comm* c, const RankParams& P, int side_streams, bool striped, cudaStream_t stream) {
   (void)stream;
   WriteValue32Fn wv = write_value_fn();
   if (!wv) return EDM_ERR_UNSUPPORTED;
@@ -778,7 +779,9 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, int side_streams, cud
   if (nstreams < 1) nstreams = 1;
   if (nstreams > edm_comm::kSideStreams) nstreams = edm_comm::kSideStreams;
   const int d_lo = P.ag_ce_lo > (P.ag_local_direct ? 1 : 0) ? P.ag_ce_lo : (P.ag_local_direct ? 1 : 0);
-  if (W - d_lo < nstreams) nstreams = W - d_lo > 0 ? W - d_lo : 1;
+  // streams are dealt by peer, or -- striped -- by chunk: then all of them serve one peer at a time
+  const int lanes = striped ? P.ag_chunks : W - d_lo;
+  if (lanes < nstreams) nstreams = lanes > 0 ? lanes : 1;
   c->streams_in_use = nstreams;
   for (int i = 0; i < nstreams; ++i) EDM_CUDA(cudaStreamWaitEvent(c->side[i], c->ev_in, 0));
   // when the shard does not cover whole row blocks the kernel also reads the own rows from the
@@ -787,12 +790,12 @@ int ag_copy_engine_issue(edm_comm* c, const RankParams& P, int side_streams, cud
   if (static_cast<size_t>(P.M) * row_bytes > c->window_bytes / 2) return EDM_ERR_CAPACITY;
   for (int d = d_lo; d < W; ++d) {
     const int peer = (P.rank - d + W) % W;
-    cudaStream_t side = c->side[d % nstreams];
     char* dst0 = static_cast<char*>(P.gather[peer]) + static_cast<size_t>(P.rank) * rows * row_bytes;
     const char* src0 = static_cast<const char*>(P.x_local);
     for (int ch = 0; ch < P.ag_chunks; ++ch) {
       const int64_t r_lo = ch * chunk_rows;
       const int64_t r_hi = r_lo + chunk_rows < rows ? r_lo + chunk_rows : rows;
+      cudaStream_t side = c->side[(striped ? ch : d) % nstreams];
       if (r_hi > r_lo) {
         if (P.ld_x == P.K)  // contiguous shard: a plain copy is the fastest thing a copy engine does
           EDM_CUDA(cudaMemcpyAsync(dst0 + r_lo * row_bytes, src0 + r_lo * row_bytes,
@@ -1071,8 +1074,86 @@ static int pusher_ctas_for(const edm_tp_call_t& call, const RankParams& P, int c
   return EDM_OK;
 }
 
+// One-shot all-reduce: fills one rank's parameters (bumping the context's call counter) and runs
+// that rank's plain GEMM into its window bank.
+static int one_shot_rank(edm_comm* c, const edm_tp_call_t& call, OneShotRank& R, cudaStream_t s) {
+  if (!c || !call.a || !call.b || !call.d) return EDM_ERR_BAD_ARG;
+  if (call.op != EDM_OP_GEMM_AR || c->world < 2 || c->world > kOneShotMaxRanks) return EDM_ERR_BAD_ARG;
+  if (call.dtype != EDM_DTYPE_BF16 && call.dtype != EDM_DTYPE_FP32) return EDM_ERR_BAD_ARG;
+  int rc = check_dims(call.M, call.N, call.K);
+  if (rc) return rc;
+  const int ob = call.dtype == EDM_DTYPE_BF16 ? 2 : 4;
+  if ((call.N * ob) & 15 || (call.ldd * ob) & 15 || call.ldd < call.N || (reinterpret_cast<uintptr_t>(call.d) & 15u))
+    return EDM_ERR_BAD_ARG;
+  const size_t need = static_cast<size_t>(call.M) * static_cast<size_t>(call.N) * ob;
+  if (need > c->window_bytes / 2) return EDM_ERR_CAPACITY;
+  for (int p = 0; p < c->world; ++p)
+    if (!c->base[p]) return EDM_ERR_BAD_ARG;  // peers not linked yet
+  const uint32_t epoch = c->epoch + 1;
+  const size_t par = epoch & 1u;
+  std::memset(&R, 0, sizeof(R));
+  for (int p = 0; p < c->world; ++p) {
+    R.part[p] = c->base[p] + c->off_window() + par * (c->window_bytes / 2);
+    R.flags[p] = reinterpret_cast<uint32_t*>(c->base[p] + c->off_flags() + par * (c->flag_bytes / 2));
+  }
+  R.out = call.d; R.ld_out = call.ldd;
+  R.M = static_cast<int32_t>(call.M); R.N = static_cast<int32_t>(call.N);
+  R.rank = c->rank; R.world = c->world; R.epoch = epoch; R.out_bytes = ob;
+  rc = plain_gemm(call.dtype, call.a, call.lda, call.b, call.ldb, const_cast<char*>(R.part[c->rank]), call.N,
+                  call.M, call.N, call.K, call.workspace, call.workspace_bytes, s);
+  if (rc) return rc;
+  c->epoch = epoch;
+  return EDM_OK;
+}
+
+// CTAs per rank of the one-shot reduction: about one 16-byte vector per thread (the kernel is a
+// single round trip of loads then), within what is co-resident.
+static int one_shot_ctas(const OneShotRank& R, int limit) {
+  const int64_t vecs = static_cast<int64_t>(R.M) * R.N * R.out_bytes / 16;
+  int64_t n = (vecs + kOneShotThreads - 1) / kOneShotThreads;
+  if (n > limit) n = limit;
+  return static_cast<int>(n < 1 ? 1 : n);
+}
+
+static int one_shot_launch(OneShotParams& lp, int n, bool coop, cudaStream_t s) {
+  lp.num_vranks = n;
+  lp.timeout_ns = g_timeout_ns;
+  dbg_reset();
+  for (int i = 0; i < n; ++i) {
+    const OneShotRank& R = lp.r[i];
+    dbg_add_matrix(R.out, R.M, R.N, R.ld_out, R.out_bytes);
+    for (int p = 0; p < R.world; ++p) {
+      dbg_add(const_cast<char*>(R.part[p]), static_cast<size_t>(R.M) * R.N * R.out_bytes);
+      dbg_add(R.flags[p], static_cast<size_t>(R.world) * 4);
+    }
+  }
+  if (int rc = dbg_publish(s)) return rc;
+  const int grid = lp.ctas_per_vrank * n;
+  if (coop) {
+    void* args[] = {&lp};
+    EDM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ar_one_shot_kernel), dim3(grid), dim3(kOneShotThreads),
+                                         args, 0, s));
+  } else {
+    ar_one_shot_kernel<<<grid, kOneShotThreads, 0, s>>>(lp);
+    EDM_CUDA(cudaGetLastError());
+  }
+  return EDM_OK;
+}
+
 int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
   if (!comm || !call) return EDM_ERR_BAD_ARG;
+  if (call->one_shot != 0 && call->one_shot != 1) return EDM_ERR_BAD_ARG;
+  if (call->one_shot && comm->world > 1) {
+    cudaStream_t s1 = static_cast<cudaStream_t>(stream);
+    if (capturing(s1)) return EDM_ERR_UNSUPPORTED;  // the flags carry the call counter (see below)
+    OneShotParams op;
+    std::memset(&op, 0, sizeof(op));
+    if (int rc = one_shot_rank(comm, *call, op.r[0], s1)) return rc;
+    const int sms = num_sms();
+    if (sms <= 0) return EDM_ERR_CUDA;
+    op.ctas_per_vrank = one_shot_ctas(op.r[0], sms);
+    return one_shot_launch(op, 1, false, s1);
+  }
   LaunchParams lp;
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1106,7 +1187,8 @@ int edm_tp_launch(edm_comm_t* comm, const edm_tp_call_t* call, void* stream) {
                            [&] { return launch_variant(call->dtype, cg, kBlockN, lp, grid, false, s); });
   if (rc) return rc;
   if (ce) {
-    if ((rc = ag_copy_engine_issue(comm, P, call->side_streams, s))) return rc;
+    if ((rc = ag_copy_engine_issue(comm, P, call->side_streams, call->transport == EDM_TRANSPORT_COPY_ENGINE_STRIPED, s)))
+      return rc;
     return ag_copy_engine_after_launch(comm, s);
   }
   return EDM_OK;
@@ -1118,6 +1200,22 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
   std::memset(&lp, 0, sizeof(lp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (capturing(s)) return EDM_ERR_UNSUPPORTED;  // see edm_tp_launch
+  if (calls[0].one_shot != 0 && calls[0].one_shot != 1) return EDM_ERR_BAD_ARG;
+  if (calls[0].one_shot && comms[0] && comms[0]->world > 1) {
+    // every rank's GEMM first, then one cooperative launch in which the ranks' CTAs exchange flags
+    OneShotParams op;
+    std::memset(&op, 0, sizeof(op));
+    for (int i = 0; i < n; ++i) {
+      if (!comms[i] || calls[i].one_shot != 1 || calls[i].dtype != calls[0].dtype || calls[i].M != calls[0].M ||
+          calls[i].N != calls[0].N)
+        return EDM_ERR_BAD_ARG;
+      if (int rc = one_shot_rank(comms[i], calls[i], op.r[i], s)) return rc;
+    }
+    const int sms = num_sms();
+    if (sms < n) return EDM_ERR_CUDA;
+    op.ctas_per_vrank = one_shot_ctas(op.r[0], sms / n);
+    return one_shot_launch(op, n, true, s);
+  }
   const int cg = pick_cta_group(calls[0].dtype, calls[0].op, calls[0].M, comms[0] ? comms[0]->world : 1);
   dbg_reset();
   for (int i = 0; i < n; ++i) {
@@ -1155,7 +1253,9 @@ int edm_tp_launch_emulated(edm_comm_t* const* comms, const edm_tp_call_t* calls,
     splits = splits || launch_splits(lp, P, calls[0].dtype, cg, kBlockN, lp.ctas_per_vrank * n);
     if (P.mode == kAG && P.world > 1 && P.ag_ce_lo < P.world) {
       if ((rc = ag_copy_engine_mark(comms[i], s))) return rc;
-      if ((rc = ag_copy_engine_issue(comms[i], P, calls[i].side_streams, s))) return rc;
+      if ((rc = ag_copy_engine_issue(comms[i], P, calls[i].side_streams,
+                                     calls[i].transport == EDM_TRANSPORT_COPY_ENGINE_STRIPED, s)))
+        return rc;
       if ((rc = ag_copy_engine_after_launch(comms[i], s))) return rc;
     }
   }

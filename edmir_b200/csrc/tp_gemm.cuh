@@ -71,6 +71,7 @@ enum Status : uint32_t {
   kTimeoutTailFlag = 8,      // split last wave: another CTA's partial sum never arrived
   kBoundsFault = 9,          // checking build only: an address outside every range the launch may touch
   kTimeoutPushCount = 10,    // AG with pusher CTAs: this rank's own pushers never finished a chunk
+  kTimeoutOneShotFlag = 11,  // one-shot AR: a peer's "partial complete" flag never arrived
 };
 
 __device__ uint32_t g_status[16];

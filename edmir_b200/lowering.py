@@ -58,6 +58,7 @@ class TPLinearSpec:
 # ---------------------------------------------------------------- candidates
 AG_PUSHER_CTAS = (4, 8, 16, 24, 32)
 AG_CHUNKS = (1, 2, 4, 8)
+ONE_SHOT_MAX_BYTES = 4 << 20   # partial [M, N] above which a one-shot all-reduce is not even scored
 
 
 def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedule]:
@@ -69,7 +70,9 @@ def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedul
     comparison baseline).  All-gather + GEMM: kernel pushes by dedicated pusher CTAs (how many SMs
     to give up) or by warps inside every GEMM CTA, copy engines on one or two side streams, or
     both, each at several flag granularities.  GEMM + reduce-scatter / all-reduce have one fused
-    schedule: every tile is pushed as it is finished, there is no coarser granularity to choose."""
+    schedule: every tile is pushed as it is finished, there is no coarser granularity to choose.
+    Small all-reduces also have the one-shot schedule (plain GEMM, then every rank reads all
+    partials): one flag round trip instead of two, W-1 times the partial as link reads."""
     if spec.world == 1:
         return [Schedule(index=0)]
     out: list[Schedule] = []
@@ -77,6 +80,8 @@ def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedul
         out.append(Schedule(fused=False))
     if spec.op != "ag_gemm":
         out.append(Schedule())
+        if spec.op == "gemm_ar" and spec.M * spec.N * 2 <= ONE_SHOT_MAX_BYTES and (spec.N * 2) % 16 == 0:
+            out.append(Schedule(one_shot=True))
     else:
         rows = spec.M // spec.world
         chunk_ok = [c for c in AG_CHUNKS if c <= rows and (rows // c) >= 1]
@@ -85,8 +90,11 @@ def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedul
                 out.append(Schedule(chunks=c, transport="sm", pusher_ctas=p))
         for c in chunk_ok[:3]:
             out.append(Schedule(chunks=c, transport="sm", pusher_ctas=0))
-            for s in (1, 2):
-                out.append(Schedule(chunks=c, transport="ce", side_streams=s))
+            # (one side stream delivers in consumption order but at ~60 % of the rate of two, and
+            # measured slower on every shape: not a candidate)
+            out.append(Schedule(chunks=c, transport="ce", side_streams=2))
+            if c >= 2:
+                out.append(Schedule(chunks=c, transport="cs", side_streams=2))
         if spec.world > 2:
             for c in chunk_ok[1:3]:
                 for p in (8, 16):
@@ -173,7 +181,8 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
     if spec.op == "ag_gemm":
         c = sched.chunks
         first_d = 1
-        ce_lo = {"sm": W, "ce": first_d, "hybrid": max(first_d, W - sched.ce_peers)}[sched.transport]
+        ce_lo = {"sm": W, "ce": first_d, "cs": first_d, "hybrid": max(first_d, W - sched.ce_peers)}[sched.transport]
+        striped = sched.transport == "cs"
         pushes = ce_lo > first_d
         uses_ce = ce_lo < W
         pushers = sched.pusher_ctas if pushes else 0
@@ -182,8 +191,9 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
         if pushes and pushers == 0:
             total = int(total * calib.sm_push_slowdown)  # push warps share the GEMM CTAs' memory pipes
         push_rate = min(calib.link_gbs, pushers * calib.pusher_cta_gbs) if pushers else calib.link_gbs
-        n_streams = min(max(sched.side_streams, 1), max(W - ce_lo, 1)) if uses_ce else 0
-        ce_rate = calib.ce_rate(n_streams, W - ce_lo) if uses_ce else 0.0
+        n_streams = min(max(sched.side_streams, 1), c if striped else max(W - ce_lo, 1)) if uses_ce else 0
+        # striped: every stream serves the same peer, the engines together reach the one-peer rate
+        ce_rate = (calib.ce_gbs_one_peer if striped else calib.ce_rate(n_streams, W - ce_lo)) if uses_ce else 0.0
         if pushes and uses_ce and push_rate + ce_rate > calib.link_gbs:  # both share the link
             scale = calib.link_gbs / (push_rate + ce_rate)
             push_rate, ce_rate = push_rate * scale, ce_rate * scale
@@ -204,10 +214,12 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
             else:
                 stream, rate, backend = f"ce{d % n_streams}", ce_rate / n_streams, "copy-engine"
             pushed = d < ce_lo
-            per_chunk = (calib.push_chunk_ns if pushers else 0) if pushed else calib.ce_op_ns
+            per_chunk = (calib.push_chunk_ns if pushers else calib.sm_chunk_ns) if pushed else calib.ce_op_ns
             publish = (calib.push_publish_ns if pushers else calib.publish_ns) if pushed else 0
             for k in range(c):
                 nbytes = shard // c + (1 if k < shard % c else 0)
+                if striped:
+                    stream = f"ce{k % n_streams}"
                 node = plan.add("comm", f"all_gather.s{d}.c{k}", comm_op, int(nbytes / rate) + per_chunk, stream=stream,
                                 after=last[stream], movement=move(nbytes, backend),
                                 attrs={**attrs, "chunk": k, "shard": d})
@@ -226,6 +238,17 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
                 if j > 0 and share < floor:
                     plan.add("compute", f"tile.s{j}.c{k}", irops.COMPUTE_GEMM, floor, deps=deps, stream=f"tiles.s{j}",
                              attrs={**attrs, "chunk": k, "shard": j})
+        return plan.build(common)
+
+    if sched.one_shot:
+        # plain GEMM, second launch, one flag round trip, then W-1 remote reads of the whole partial
+        setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew, stream="compute")
+        g = plan.add("compute", "gemm", irops.COMPUTE_GEMM, gemm_ns(spec.M, spec.N, spec.K, calib), stream="compute",
+                     after=setup, attrs=dict(attrs))
+        flag = plan.add("other", "flags", irops.EVENT_RECORD, calib.one_shot_sync_ns, deps=(g,), stream="push.flags")
+        pull = (W - 1) * spec.M * spec.N * 2
+        plan.add("comm", "gemm_ar.pull", comm_op, int(pull / calib.all_to_all_rate(W)), deps=(flag,), stream="push",
+                 movement=move(pull, "nvlink-p2p"), attrs=dict(attrs))
         return plan.build(common)
 
     # GEMM + reduce-scatter / all-reduce: tiles are pushed as they finish; modelled as G groups of

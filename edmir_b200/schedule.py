@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, replace
 
-TRANSPORTS = ("sm", "ce", "hybrid")
+TRANSPORTS = ("sm", "ce", "hybrid", "cs")
 
 
 @dataclass(frozen=True)
@@ -19,12 +19,14 @@ class Schedule:
     index: int = 0
     fused: bool = True       # False: GEMM kernel, then a separate library collective (comparison baseline)
     chunks: int = 1          # all-gather: flag granularity, chunks per shard
-    transport: str = "sm"    # all-gather: "sm" kernel pushes, "ce" copy engines, "hybrid" both
+    transport: str = "sm"    # all-gather: "sm" kernel pushes, "ce" copy engines (a stream per peer), "hybrid" both,
+                             # "cs" copy engines striped (a stream per chunk: all engines on one peer at a time)
     pusher_ctas: int = 0     # all-gather, kernel pushes: CTAs that only push (0: push warps in every GEMM CTA)
     ce_peers: int = 0        # all-gather, hybrid: how many of the farthest peers the copy engines serve
     side_streams: int = 2    # all-gather, copy engines: streams the copies are spread over
     band_rows: int = 0       # tile walk: row blocks per band (0: library default)
     band_cols: int = 0       # tile walk: column blocks per super-tile (0: whole width)
+    one_shot: bool = False   # all-reduce: plain GEMM, then every rank adds up all partials itself (decode-sized M)
 
     def __post_init__(self) -> None:
         if self.transport not in TRANSPORTS:
@@ -38,8 +40,10 @@ class Schedule:
     def label(self) -> str:
         if not self.fused:
             return "unfused"
+        if self.one_shot:
+            return "oneshot"
         bits = [self.transport]
-        if self.transport != "ce":
+        if self.transport not in ("ce", "cs"):
             bits.append(f"p{self.pusher_ctas}")
         if self.transport == "hybrid":
             bits.append(f"ce{self.ce_peers}")

@@ -23,7 +23,7 @@ from .schedule import Schedule
 
 _OPS = {"gemm_rs": _lib.EDM_OP_GEMM_RS, "gemm_ar": _lib.EDM_OP_GEMM_AR, "ag_gemm": _lib.EDM_OP_AG_GEMM}
 _TRANSPORTS = {"sm": _lib.EDM_TRANSPORT_SM, "ce": _lib.EDM_TRANSPORT_COPY_ENGINE,
-               "hybrid": _lib.EDM_TRANSPORT_HYBRID}
+               "hybrid": _lib.EDM_TRANSPORT_HYBRID, "cs": _lib.EDM_TRANSPORT_COPY_ENGINE_STRIPED}
 _DTYPES = {torch.bfloat16: _lib.EDM_DTYPE_BF16, torch.float32: _lib.EDM_DTYPE_FP32}
 
 
@@ -147,6 +147,9 @@ class SymmetricContext:
         call.transport = _TRANSPORTS[sched.transport]
         call.pusher_ctas, call.ce_peers, call.side_streams = sched.pusher_ctas, sched.ce_peers, sched.side_streams
         call.band_rows, call.band_cols = sched.band_rows, sched.band_cols
+        if sched.one_shot and op != "gemm_ar":
+            raise ValueError("one_shot is a schedule of gemm_ar")
+        call.one_shot = 1 if sched.one_shot else 0
         if a.dtype == torch.float32:
             need = int(self._lib.edm_gemm_fp32_workspace_bytes(a.shape[0], N, K))
             if self._workspace is None or self._workspace.numel() < need:
@@ -176,9 +179,14 @@ class SymmetricContext:
     def gemm_ar(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
                 schedule: Schedule | None = None) -> torch.Tensor:
         """Row-parallel linear + all-reduce: every rank ends with ``sum_r a_r @ b_r^T``.  ``out``
-        must come from ``self.empty`` (peers store reduced tiles straight into it)."""
+        must come from ``self.empty`` (peers store reduced tiles straight into it), except with a
+        ``one_shot`` schedule -- this rank's GEMM into the window, then one kernel in which every
+        rank adds up all partials itself -- which writes any device tensor."""
         if out is None:
-            out = self.empty((a.shape[0], b.shape[0]), a.dtype)
+            if schedule is not None and schedule.one_shot:
+                out = torch.empty((a.shape[0], b.shape[0]), dtype=a.dtype, device=a.device)
+            else:
+                out = self.empty((a.shape[0], b.shape[0]), a.dtype)
         return self._launch("gemm_ar", a, b, out, schedule)
 
     def ag_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,

@@ -60,6 +60,10 @@ extern "C" {
 /* HYBRID: the `ce_peers` farthest peers (rank-d for the largest d; their consumers need the shard
  * last) are served by copy engines, the nearer ones by the kernel. */
 #define EDM_TRANSPORT_HYBRID 2
+/* COPY_ENGINE_STRIPED: copy engines only, but the chunks of one shard are dealt over the side
+ * streams, so all engines serve the same peer at a time (every GPU sends to one peer and receives
+ * from one peer at any moment) instead of one peer per stream.  Wants chunks >= side_streams. */
+#define EDM_TRANSPORT_COPY_ENGINE_STRIPED 3
 
 #define EDM_MAX_RANKS 8
 #define EDM_IPC_HANDLE_BYTES 64
@@ -217,7 +221,8 @@ typedef struct {
   int32_t side_streams; /* AG_GEMM, copy engines: streams the copies are spread over (1 .. 4; 0 = 2) */
   int32_t band_rows;    /* tile walk: row blocks per band (0 = default) */
   int32_t band_cols;    /* tile walk: column blocks per super-tile of a band (0 = the whole width) */
-  int32_t reserved;
+  int32_t one_shot;     /* GEMM_AR: 1 = plain GEMM into the window, then a one-shot all-reduce (every rank reads
+                           all partials: for decode-sized M; d may be any device memory); 0 = fused kernel */
 } edm_tp_call_t;
 
 /* Not capturable: the flags of the exchange carry the context's call counter, which a graph replay

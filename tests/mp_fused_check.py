@@ -47,22 +47,27 @@ def main() -> int:
              ("ag_gemm", 256 * world, 520, 512, torch.bfloat16, 2),
              ("ag_gemm", 64 * world, 256, 128, torch.bfloat16, 1),
              ("ag_gemm_ce", 256 * world, 520, 512, torch.bfloat16, 2),
+             ("ag_gemm_cs", 256 * world, 520, 512, torch.bfloat16, 2),
              ("ag_gemm_push", 256 * world, 520, 512, torch.bfloat16, 2),
              ("ag_gemm_push", 64 * world, 256, 136, torch.bfloat16, 1),
              ("ag_gemm_hybrid", 256 * world, 264, 512, torch.bfloat16, 2),
-             ("gemm_ar", 256, 1024, 512, torch.float32, 1)]
+             ("gemm_ar", 256, 1024, 512, torch.float32, 1),
+             ("gemm_ar_oneshot", 1, 4096, 1792, torch.bfloat16, 1),
+             ("gemm_ar_oneshot", 48, 1032, 264, torch.bfloat16, 1),
+             ("gemm_ar_oneshot", 128, 1024, 512, torch.float32, 1)]
     if big:
         cases += [("gemm_rs", 8192, 8192, 1024, torch.bfloat16, 1), ("ag_gemm", 8192, 1280, 8192, torch.bfloat16, 4),
-                  ("ag_gemm_ce", 8192, 1280, 8192, torch.bfloat16, 2), ("ag_gemm_push", 8192, 1280, 8192, torch.bfloat16, 4),
+                  ("ag_gemm_ce", 8192, 1280, 8192, torch.bfloat16, 2), ("ag_gemm_cs", 8192, 1280, 8192, torch.bfloat16, 4), ("ag_gemm_push", 8192, 1280, 8192, torch.bfloat16, 4),
                   ("ag_gemm_hybrid", 8192, 2048, 8192, torch.bfloat16, 2), ("gemm_ar", 1024, 4096, 14336 // world, torch.bfloat16, 1)]
-    schedules = {"": Schedule(transport="sm"), "_ce": Schedule(transport="ce"),
+    schedules = {"": Schedule(transport="sm"), "_ce": Schedule(transport="ce"), "_cs": Schedule(transport="cs"),
                  "_push": Schedule(transport="sm", pusher_ctas=16),
-                 "_hybrid": Schedule(transport="hybrid", pusher_ctas=8, ce_peers=max(1, (world - 1) // 2), side_streams=1)}
+                 "_hybrid": Schedule(transport="hybrid", pusher_ctas=8, ce_peers=max(1, (world - 1) // 2), side_streams=1),
+                 "_oneshot": Schedule(one_shot=True)}
     for idx, (op, M, N, K, dtype, chunks) in enumerate(cases):
         wscale = 1.0 if dtype == torch.float32 else 0.02
-        suffix = next((k for k in ("_ce", "_push", "_hybrid") if op.endswith(k)), "")
+        suffix = next((k for k in ("_ce", "_cs", "_push", "_hybrid", "_oneshot") if op.endswith(k)), "")
         op = op[:len(op) - len(suffix)] if suffix else op
-        sched = dataclasses.replace(schedules[suffix], chunks=chunks)
+        sched = dataclasses.replace(schedules[suffix], chunks=chunks) if op == "ag_gemm" else schedules[suffix]
         rows = M // world if op == "ag_gemm" else M
         a_all = [rand((rows, K), 1.0, dtype, 1000 * idx + r) for r in range(world)]
         b_all = [rand((N, K), wscale, dtype, 1000 * idx + 500 + r) for r in range(world)]
@@ -86,7 +91,7 @@ def main() -> int:
             if op == "gemm_rs":
                 out = ctx.gemm_rs(a, b)
             elif op == "gemm_ar":
-                out = ctx.gemm_ar(a, b, out)
+                out = ctx.gemm_ar(a, b, out, schedule=sched)
             else:
                 out = ctx.ag_gemm(a, b, schedule=sched)
             torch.cuda.synchronize()

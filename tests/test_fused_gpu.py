@@ -107,9 +107,119 @@ def test_config1_all_reduce_fp32(cuda_clean, group_factory):
         assert torch.equal(outs[0], outs[1])
 
 
+ONE_SHOT = Schedule(one_shot=True)
+
+
+@pytest.mark.parametrize("world,M,N,K", [(2, 1, 4096, 1792), (2, 64, 4096, 1792), (4, 16, 4096, 3584),
+                                         (3, 128, 520, 264), (4, 300, 1032, 512)])
+def test_one_shot_all_reduce_bf16(cuda_clean, group_factory, world, M, N, K):
+    # plain GEMM into the window, then every rank adds up all partials itself: outputs need not be
+    # symmetric, every rank holds the same bits, and those are exactly the fp32 sum in rank order
+    # of the ranks' bf16 GEMM results
+    g = group_factory(world)
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for call in range(4):  # both window banks twice
+        a = [_rand((M, K), 1.0, torch.bfloat16, 1300 + 10 * call + r) for r in range(world)]
+        b = [_rand((N, K), 0.02, torch.bfloat16, 1400 + 10 * call + r) for r in range(world)]
+        want = oracle.gemm_all_reduce([_np(x) for x in a], [_np(x) for x in b])[0]
+        a_d, b_d = [x.cuda() for x in a], [x.cuda() for x in b]
+        _poison(g, outs)
+        g.run("gemm_ar", a_d, b_d, outs, schedule=ONE_SHOT)
+        torch.cuda.synchronize()
+        acc = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+        for r in range(world):
+            acc += linear.gemm(a_d[r], b_d[r]).float()
+        for r in range(world):
+            assert oracle.rel_l2(_np(outs[r]), want) <= BF16_TOL, (call, r)
+            assert torch.equal(outs[r], acc.to(torch.bfloat16)), (call, r)
+    assert linear.status()[0] == 0
+
+
+def test_one_shot_all_reduce_fp32_and_strided_output(cuda_clean, group_factory):
+    g = group_factory(2)
+    a_sh, b_sh = oracle.config1_inputs()
+    want = oracle.config1_output(a_sh, b_sh)
+    a_d = [torch.from_numpy(a).cuda() for a in a_sh]
+    b_d = [torch.from_numpy(np.ascontiguousarray(b.T)).cuda() for b in b_sh]
+    wide = [torch.zeros(256, 1024 + 64, dtype=torch.float32, device="cuda") for _ in range(2)]
+    outs = [w[:, :1024] for w in wide]  # row stride larger than the width
+    for call in range(2):
+        g.poison()
+        for w in wide:
+            w.fill_(7.0)
+        g.run("gemm_ar", a_d, b_d, outs, schedule=ONE_SHOT)
+        torch.cuda.synchronize()
+        for r in range(2):
+            assert oracle.rel_l2(outs[r].cpu().numpy(), want) <= FP32_TOL, (call, r)
+            assert torch.all(wide[r][:, 1024:] == 7.0)  # nothing written past the row's end
+        assert torch.equal(outs[0], outs[1])
+
+
+def test_one_shot_and_fused_all_reduce_alternate_on_one_context(cuda_clean, group_factory):
+    # both kinds share the window banks and flag words of the context, call after call
+    world, N, K = 4, 2048, 512
+    g = group_factory(world)
+    for step, (M, sched) in enumerate([(16, ONE_SHOT), (256, None), (16, ONE_SHOT), (16, ONE_SHOT), (48, None),
+                                       (128, ONE_SHOT)]):
+        a = [_rand((M, K), 1.0, torch.bfloat16, 1500 + 10 * step + r) for r in range(world)]
+        b = [_rand((N, K), 0.02, torch.bfloat16, 1600 + 10 * step + r) for r in range(world)]
+        want = oracle.gemm_all_reduce([_np(x) for x in a], [_np(x) for x in b])[0]
+        outs = [ctx.empty((M, N), torch.bfloat16) for ctx in g.ranks]
+        _poison(g, outs)
+        g.run("gemm_ar", [x.cuda() for x in a], [x.cuda() for x in b], outs, schedule=sched)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert oracle.rel_l2(_np(outs[r]), want) <= BF16_TOL, (step, r)
+        for ctx in g.ranks:
+            ctx.reset_heap()
+
+
+def test_one_shot_rejects_what_it_cannot_run(cuda_clean):
+    g = symm.EmulatedGroup(2, 1 << 20, 1 << 20)
+    try:
+        a = [torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        b = [torch.zeros(8192, 64, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        outs = [torch.zeros(64, 8192, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        with pytest.raises(_lib.EdmError) as err:   # the partial (1 MiB) does not fit half of the window
+            g.run("gemm_ar", a, b, outs, schedule=ONE_SHOT)
+        assert err.value.code == _lib.EDM_ERR_CAPACITY
+        b4 = [torch.zeros(36, 64, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        o4 = [torch.zeros(64, 36, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        with pytest.raises(ValueError):             # rows are not whole 16-byte vectors
+            g.run("gemm_ar", a, b4, o4, schedule=ONE_SHOT)
+        with pytest.raises(ValueError):
+            g.ranks[0]._call("gemm_rs", a[0], b[0], torch.zeros(32, 8192, dtype=torch.bfloat16, device="cuda"), ONE_SHOT)
+    finally:
+        g.close()
+
+
+def test_one_shot_missing_peer_times_out_and_context_survives(group_factory):
+    # rank 0 of a 2-rank group runs alone: its peer's flag never comes, the bounded wait gives up with
+    # its own status code and nothing is added up
+    assert torch.cuda.is_available()
+    linear.clear_status()
+    g = group_factory(2)
+    a = _rand((16, 256), 1.0, torch.bfloat16, 41).cuda()
+    b = _rand((512, 256), 0.02, torch.bfloat16, 42).cuda()
+    out = torch.full((16, 512), 3.0, dtype=torch.bfloat16, device="cuda")
+    linear.set_timeout_ms(50)
+    try:
+        g.ranks[0].gemm_ar(a, b, out, schedule=ONE_SHOT)
+        st = linear.status()
+    finally:
+        linear.set_timeout_ms(2000)
+        linear.clear_status()
+    assert st[0] == 11, st[:8]
+    assert torch.all(out == 3.0)
+    got = linear.gemm(a, b)
+    assert oracle.rel_l2(_np(got), oracle.gemm(_np(a), _np(b))) <= BF16_TOL
+    assert linear.status()[0] == 0
+
+
 AG_SCHEDULES = {
     "sm": dict(transport="sm"),                                    # push warps inside every GEMM CTA
     "ce": dict(transport="ce"),                                    # copy engines only
+    "striped": dict(transport="cs"),                               # copy engines, a stream per chunk
     "pushers": dict(transport="sm", pusher_ctas=4),                # CTAs that only push
     "hybrid": dict(transport="hybrid", pusher_ctas=2, ce_peers=1, side_streams=1),  # farthest peer by copy engine
 }

@@ -42,7 +42,8 @@ def test_candidates():
     assert not scheds[0].fused and all(s.fused for s in scheds[1:])
     # a fused one-chunk schedule exists and is not the unfused one
     assert any(s.fused and s.chunks == 1 for s in scheds)
-    assert {s.transport for s in scheds[1:]} == {"sm", "ce", "hybrid"}
+    assert {s.transport for s in scheds[1:]} == {"sm", "ce", "hybrid", "cs"}
+    assert all(s.chunks >= 2 for s in scheds if s.transport == "cs")
     assert {s.pusher_ctas for s in scheds if s.transport == "sm"} == {0, 4, 8, 16, 24, 32}
     # two-row shards cannot be cut into more than two chunks; two ranks have no far peers
     tiny = lowering.candidates(lowering.TPLinearSpec("ag_gemm", 16, 64, 64, 8))
@@ -51,6 +52,12 @@ def test_candidates():
     # reduce-scatter / all-reduce: unfused and the one fused schedule; one rank: nothing to choose
     assert [s.fused for s in lowering.candidates(lowering.TPLinearSpec("gemm_rs", 8192, 8192, 1024, 8))] == [False, True]
     assert lowering.candidates(lowering.TPLinearSpec("gemm_rs", 128, 64, 64, 1)) == [Schedule(index=0)]
+    # decode-sized all-reduces can also run one-shot; large ones and reduce-scatters cannot
+    small = lowering.candidates(lowering.TPLinearSpec("gemm_ar", 16, 4096, 1792, 8))
+    assert [s.label() for s in small] == ["unfused", "sm-p0-c1", "oneshot"] and small[2].one_shot
+    assert not any(s.one_shot for s in lowering.candidates(lowering.TPLinearSpec("gemm_ar", 8192, 4096, 1792, 8)))
+    assert not any(s.one_shot for s in lowering.candidates(lowering.TPLinearSpec("gemm_rs", 64, 4096, 1792, 8)))
+    assert not any(s.one_shot for s in lowering.candidates(lowering.TPLinearSpec("gemm_ar", 16, 36, 64, 2)))
     with pytest.raises(ValueError):
         lowering.TPLinearSpec("gemm_rs", 100, 64, 64, 8)
     with pytest.raises(ValueError):
@@ -60,7 +67,8 @@ def test_candidates():
 
 
 @pytest.mark.parametrize("op,M,N,K,world", [("ag_gemm", 8192, 1280, 8192, 8), ("ag_gemm", 8192, 7168, 8192, 2),
-                                            ("gemm_rs", 8192, 8192, 1024, 8), ("gemm_ar", 128, 4096, 1792, 4)])
+                                            ("gemm_rs", 8192, 8192, 1024, 8), ("gemm_ar", 128, 4096, 1792, 4),
+                                            ("gemm_ar", 1024, 4096, 1792, 8)])
 def test_selection_is_the_native_critical_path_of_each_candidate_graph(native_lib, op, M, N, K, world):
     spec = lowering.TPLinearSpec(op, M, N, K, world)
     sel = lowering.select_schedule(spec, Calibration())
