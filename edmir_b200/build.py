@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libedm_b200.so")
 SOURCES = ["edm_api.cu", "selector.cpp"]
-HEADERS = ["ptx.cuh", "tp_gemm.cuh", "moe.cuh", "ar_oneshot.cuh", os.path.join("..", "..", "include", "edm_b200.h")]
+HEADERS = ["ptx.cuh", "tp_gemm.cuh", "moe.cuh", "ar_oneshot.cuh", "decode_gemm.cuh", os.path.join("..", "..", "include", "edm_b200.h")]
 
 
 def _nvcc() -> str:

@@ -34,6 +34,8 @@ class Calibration:
     ``push_chunk_ns``: what a chunk boundary costs the pusher warps (their pipelines drain);
     ``sm_chunk_ns``: what it costs push warps inside the GEMM CTAs (a fence on a busy SM per flag);
     ``one_shot_sync_ns``: one-shot all-reduce -- second launch, fence, flag flight, first remote load;
+    ``decode_fixed_ns`` / ``decode_gbs``: decode kernel (GEMMs of up to 64 rows): launch to first MMA
+    plus the cluster reduction, and the rate at which it streams the weights;
     ``push_publish_ns``: latency from "all pusher warps have counted a chunk" to "flag visible".
     ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
     ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams when the
@@ -62,6 +64,8 @@ class Calibration:
     push_chunk_ns: int = 1_500
     sm_chunk_ns: int = 4_500
     one_shot_sync_ns: int = 8_000
+    decode_fixed_ns: int = 8_000
+    decode_gbs: float = 6000.0
     push_publish_ns: int = 5_000
     ag_link_gbs: float = 470.0
     sm_push_slowdown: float = 1.17
@@ -136,9 +140,14 @@ def last_wave(tiles: int, units: int, k_blocks: int) -> float:
     return 1.0 if parts < 2 else 1.0 / parts + 0.15
 
 
-def gemm_ns(M: int, N: int, K: int, calib: Calibration, units: int | None = None, elem_bytes: int = 2) -> int:
+def gemm_ns(M: int, N: int, K: int, calib: Calibration, units: int | None = None, elem_bytes: int = 2,
+            plain: bool = False) -> int:
     """Time of the GEMM alone on ``units`` CTA pairs: whole waves of 256x256 tiles plus the last
-    one (see ``last_wave``), but never less than the flops at the calibrated rate."""
+    one (see ``last_wave``), but never less than the flops at the calibrated rate.  ``plain``: a
+    launch without an exchange, which runs the decode kernel for up to 64 rows (the weights
+    streamed once at ``decode_gbs`` plus a fixed cost)."""
+    if plain and M <= 64 and -(-N // 128) <= 2 * calib.gemm_units:
+        return int(calib.decode_fixed_ns + N * K * elem_bytes / calib.decode_gbs)
     units = calib.gemm_units if units is None else max(units, 1)
     tiles = -(-M // 256) * -(-N // 256)
     k_blocks = -(-K * elem_bytes // 128)

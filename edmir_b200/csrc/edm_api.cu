@@ -13,6 +13,7 @@
 #include "tp_gemm.cuh"
 #include "moe.cuh"
 #include "ar_oneshot.cuh"
+#include "decode_gemm.cuh"
 
 using namespace edm;
 
@@ -36,10 +37,12 @@ int current_device() {
 // EDM_BAND / EDM_BAND_COLS (row blocks per band of the tile walk / column blocks per super-tile), EDM_PUSH_STRIDE (every n-th CTA pushes all-gather
 // shards with the sm transport), EDM_SIDE_STREAMS (copy-engine transport), EDM_CTA_GROUP (1 or 2),
 // EDM_BLOCK_N (32 or 256: tile width of the single-CTA plain GEMM), EDM_TAIL_SPLIT (most pieces a
-// tile of an incomplete last wave is cut into along K; 0 or 1: none).
+// tile of an incomplete last wave is cut into along K; 0 or 1: none), EDM_DECODE (most rows a GEMM
+// may have to run the decode kernel instead of the general one; 0: never).
+constexpr int kDecodeMaxRows = 64;  // beyond that the general kernel is as fast (measured at 96 and 128 rows)
 struct Tuning {
   int stage_limit = 0, band = 0, band_cols = 0, push_stride = 1, side_streams = 2, cta_group = 0, block_n = 0,
-      tail_split = kTailMaxParts;
+      tail_split = kTailMaxParts, decode = kDecodeMaxRows;
   Tuning() {
     auto get = [](const char* name, int dflt) {
       const char* e = std::getenv(name);
@@ -54,6 +57,7 @@ struct Tuning {
     cta_group = get("EDM_CTA_GROUP", 0);
     block_n = get("EDM_BLOCK_N", 0);
     tail_split = get("EDM_TAIL_SPLIT", kTailMaxParts);
+    decode = get("EDM_DECODE", kDecodeMaxRows);
   }
 };
 const Tuning& tuning() {
@@ -457,6 +461,58 @@ int launch_with_scratch(bool uses_scratch, cudaStream_t s, F&& launch) {
   return EDM_OK;
 }
 
+// Decode kernel (decode_gemm.cuh): bf16, at most 64 rows, and no more 128-column tiles than SMs
+// (every piece of every tile is resident at once; wider outputs take the general kernel).
+// `split`: pieces a tile's K range is cut into -- as many as fill the GPU, each at least 4 K blocks.
+int decode_tok(int64_t M) { return M <= 32 ? 32 : 64; }
+bool decode_plan(int dtype, int64_t M, int64_t N, int64_t K, int sms, int* tiles_out, int* split_out) {
+  if (dtype != EDM_DTYPE_BF16 || M > kDecodeMaxRows || M > tuning().decode || K % 8 || N % 8) return false;
+  const int64_t tiles = (N + kBlockM - 1) / kBlockM;
+  if (tiles > sms) return false;
+  const int64_t kb = (K * 2 + kBlockKBytes - 1) / kBlockKBytes;
+  const int tok = decode_tok(M);
+  const int max_split = tok == 32 ? DecodeShape<32>::kMaxSplit : DecodeShape<64>::kMaxSplit;
+  int split = 1;
+  while (split * 2 <= max_split && tiles * split * 2 <= sms && kb / (split * 2) >= 4) split *= 2;
+  *tiles_out = static_cast<int>(tiles);
+  *split_out = split;
+  return true;
+}
+
+int decode_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd, int64_t M, int64_t N,
+                int64_t K, int tiles, int split, cudaStream_t s) {
+  DecodeParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc;
+  if ((rc = make_tmap(&p.tmap_w, b, N, K, ldb, 2, kBlockM))) return rc;
+  const int tok = decode_tok(M);
+  if ((rc = make_tmap(&p.tmap_x, a, M, K, lda, 2, tok))) return rc;
+  p.out = d; p.ld_out = ldd;
+  p.M = static_cast<int32_t>(M); p.N = static_cast<int32_t>(N); p.K = static_cast<int32_t>(K);
+  p.split = split;
+  p.timeout_ns = g_timeout_ns;
+  void* fn = tok == 32 ? reinterpret_cast<void*>(decode_gemm_kernel<32>) : reinterpret_cast<void*>(decode_gemm_kernel<64>);
+  static std::atomic<bool> configured[kMaxDevices][2] = {};
+  const int dev = current_device();
+  if (dev < 0) return EDM_ERR_UNSUPPORTED;
+  std::atomic<bool>& done = configured[dev][tok == 32 ? 0 : 1];
+  if (!done.load(std::memory_order_acquire)) {
+    EDM_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes));
+    done.store(true, std::memory_order_release);
+  }
+  dbg_reset();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * split); cfg.blockDim = dim3(kDecThreads); cfg.dynamicSmemBytes = kDecSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = split; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  void* args[1] = {&p};
+  EDM_CUDA(cudaLaunchKernelExC(&cfg, fn, args));
+  return EDM_OK;
+}
+
 int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* d, int64_t ldd,
                int64_t M, int64_t N, int64_t K, void* ws, size_t ws_bytes, void* stream) {
   if (!a || !b || !d) return EDM_ERR_BAD_ARG;
@@ -476,6 +532,9 @@ int plain_gemm(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb
   const int cg = pick_cta_group(dtype, EDM_OP_GEMM, M, 1);
   const int sms = num_sms();
   if (sms <= 0) return EDM_ERR_CUDA;
+  int dec_tiles = 0, dec_split = 0;
+  if (decode_plan(dtype, M, N, K, sms, &dec_tiles, &dec_split))
+    return decode_gemm(a, lda, b, ldb, d, ldd, M, N, K, dec_tiles, dec_split, s);
   const int bn = pick_block_n(dtype, cg, M, N, K, sms, max_tail_parts(s));
   rc = prepare_operands(P, dtype, cg, bn, a, lda, M, b, ldb, N, K, ws, ws_bytes, s);
   if (rc) return rc;
@@ -1009,6 +1068,12 @@ int edm_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int32_t out[4]) {
   if (!out || sms < 2 || sms > 4096) return EDM_ERR_BAD_ARG;
   int rc = check_dims(M, N, K);
   if (rc) return rc;
+  int dec_tiles = 0, dec_split = 0;
+  if (decode_plan(EDM_DTYPE_BF16, M, N, K, sms, &dec_tiles, &dec_split)) {
+    // decode kernel: tiles of all rows x 128 columns, each cut into `split` pieces along K
+    out[0] = 1; out[1] = kBlockM; out[2] = dec_tiles * dec_split; out[3] = dec_split;
+    return EDM_OK;
+  }
   const int max_parts = tuning().tail_split;
   const int cg = pick_cta_group(EDM_DTYPE_BF16, EDM_OP_GEMM, M, 1);
   const int bn = pick_block_n(EDM_DTYPE_BF16, cg, M, N, K, sms, max_parts);

@@ -166,7 +166,7 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
     if not sched.fused:
         # two launches: the library collective at its own rate, before (all-gather) or after the GEMM
         coll = calib.launch_ns + int(wire / calib.nccl_gbs) + W * calib.skew_ns_per_rank
-        full = gemm_ns(spec.M, spec.N, spec.K, calib)
+        full = gemm_ns(spec.M, spec.N, spec.K, calib, plain=spec.op != "ag_gemm")
         if spec.op == "ag_gemm":
             m = plan.add("comm", "all_gather", comm_op, coll, stream="nccl", movement=move(wire, "nccl"), attrs=dict(attrs))
             plan.add("compute", "gemm", irops.COMPUTE_GEMM, calib.launch_ns + full, deps=(m,), stream="compute",
@@ -243,8 +243,8 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
     if sched.one_shot:
         # plain GEMM, second launch, one flag round trip, then W-1 remote reads of the whole partial
         setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew, stream="compute")
-        g = plan.add("compute", "gemm", irops.COMPUTE_GEMM, gemm_ns(spec.M, spec.N, spec.K, calib), stream="compute",
-                     after=setup, attrs=dict(attrs))
+        g = plan.add("compute", "gemm", irops.COMPUTE_GEMM, gemm_ns(spec.M, spec.N, spec.K, calib, plain=True),
+                     stream="compute", after=setup, attrs=dict(attrs))
         flag = plan.add("other", "flags", irops.EVENT_RECORD, calib.one_shot_sync_ns, deps=(g,), stream="push.flags")
         pull = (W - 1) * spec.M * spec.N * 2
         plan.add("comm", "gemm_ar.pull", comm_op, int(pull / calib.all_to_all_rate(W)), deps=(flag,), stream="push",

@@ -41,6 +41,31 @@ def test_gemm_bf16_matches_oracle(cuda_clean, M, N, K):
     assert oracle.rel_l2(out.float().cpu().numpy(), want) <= BF16_TOL
 
 
+@pytest.mark.parametrize("M", [1, 7, 16, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(4096, 1792), (520, 264), (4096, 14336), (128, 64), (17920, 512), (1024, 8192),
+                                 (136, 8)])
+def test_decode_kernel_matches_oracle(cuda_clean, M, N, K):
+    # few tokens: weights on the MMA's M side, a cluster of CTAs per 128-column tile cutting K.
+    # Strided tokens, ragged N and K, a row stride wider than the output, and guard rows around it.
+    if linear.gemm_plan(M, N, K)["block_n"] != 128:
+        pytest.skip("this row count runs the general kernel")
+    a_wide = _rand((M, K + 24), 1.0, torch.bfloat16, 11).cuda()
+    a = a_wide[:, :K]
+    b = _rand((N, K), 0.02, torch.bfloat16, 12).cuda()
+    guard = torch.full((M + 2, N + 8), 5.0, dtype=torch.bfloat16, device="cuda")
+    out = guard[1:M + 1, :N]
+    first = None
+    for _ in range(3):
+        linear.gemm(a, b, out)
+        torch.cuda.synchronize()
+        first = out.clone() if first is None else first
+        assert torch.equal(out, first)          # fixed summation order: repeatable bit for bit
+    want = oracle.gemm(a.float().cpu().numpy(), b.float().cpu().numpy())
+    assert oracle.rel_l2(out.float().cpu().numpy(), want) <= BF16_TOL
+    assert torch.all(guard[0] == 5.0) and torch.all(guard[M + 1] == 5.0) and torch.all(guard[:, N:] == 5.0)
+    assert linear.status()[0] == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 1024, 512), (300, 520, 260), (4, 4, 4), (128, 256, 2048)])
 def test_gemm_fp32_matches_oracle(cuda_clean, M, N, K):
     a = _rand((M, K), 1.0, torch.float32, 3)

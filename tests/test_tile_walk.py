@@ -138,11 +138,19 @@ def test_launch_plans_of_the_layer_and_of_decode_shapes(native_lib):
     assert plan(8192, 7168, 8192) == (2, 256, 148, 8)
     assert plan(8192, 8192, 1024) == (2, 256, 148, 1)
     assert plan(8192, 8192, 3584) == (2, 256, 148, 1)
-    # decode rows of the 8B down_proj: split-K over 128 CTAs for long K, narrow tiles for short K
-    assert plan(16, 4096, 14336) == (1, 256, 128, 8)
+    # decode rows of the 8B down_proj.  Up to 64 tokens: the decode kernel, 32 tiles of 128 columns
+    # each cut into 4 pieces along K (one cluster per tile); 8 tiles are cut into 8; more tiles than
+    # fit twice are not cut; more tiles than SMs take the general kernel
+    assert plan(16, 4096, 14336) == (1, 128, 128, 4)
+    assert plan(1, 4096, 1792) == (1, 128, 128, 4)
+    assert plan(32, 1024, 8192) == (1, 128, 64, 8)
+    assert plan(8, 16384, 512) == (1, 128, 128, 1)
+    assert plan(8, 32768, 512)[1] != 128
+    assert plan(64, 4096, 7168) == (1, 128, 128, 4)
+    assert plan(65, 4096, 7168) == (1, 256, 128, 8)
+    # 128 tokens: split-K over 128 CTAs for long K, narrow tiles for short K
     assert plan(128, 4096, 7168) == (1, 256, 128, 8)
     assert plan(128, 4096, 1792) == (1, 32, 128, 1)
-    assert plan(1, 4096, 1792) == (1, 32, 128, 1)
     # 64 pair tiles on 74 pairs: nothing to cut
     assert plan(1024, 4096, 3584) == (2, 256, 128, 1)
     with pytest.raises(ValueError):
