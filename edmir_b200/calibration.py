@@ -35,7 +35,8 @@ class Calibration:
     ``sm_chunk_ns``: what it costs push warps inside the GEMM CTAs (a fence on a busy SM per flag);
     ``one_shot_sync_ns``: one-shot all-reduce -- second launch, fence, flag flight, first remote load;
     ``decode_fixed_ns`` / ``decode_gbs``: decode kernel (GEMMs of up to 64 rows): launch to first MMA
-    plus the cluster reduction, and the rate at which it streams the weights;
+    plus the cluster reduction, and the rate at which it streams the weights; ``row_block_*``: the
+    same two figures for 65 to 128 rows on the general kernel;
     ``push_publish_ns``: latency from "all pusher warps have counted a chunk" to "flag visible".
     ``pusher_cta_gbs``: what one CTA that only pushes delivers (bulk copies through shared memory).
     ``ce_gbs``: what the copy engines deliver per direction with 1, 2, ... side streams when the
@@ -66,6 +67,8 @@ class Calibration:
     one_shot_sync_ns: int = 8_000
     decode_fixed_ns: int = 8_000
     decode_gbs: float = 6000.0
+    row_block_fixed_ns: int = 14_500
+    row_block_gbs: float = 5100.0
     push_publish_ns: int = 5_000
     ag_link_gbs: float = 470.0
     sm_push_slowdown: float = 1.17
@@ -100,10 +103,14 @@ class Calibration:
         return float(self.link_gbs + f * (self.fabric_gbs - self.link_gbs))
 
     def ce_rate(self, side_streams: int, peers: int = 7) -> float:
+        """Copy-engine rate per direction: the single-peer rate at one peer, the table (measured
+        with seven peers) from seven on, linear in between (three peers: 229.6 us measured for the
+        qkv all-gather at four ranks, 226 us with this interpolation)."""
         if peers <= 1:
             return float(self.ce_gbs_one_peer)
         n = min(max(side_streams, 1), len(self.ce_gbs))
-        return float(self.ce_gbs[n - 1])
+        f = min(peers - 1, 6) / 6.0
+        return float(self.ce_gbs_one_peer + f * (self.ce_gbs[n - 1] - self.ce_gbs_one_peer))
 
 
 def wire_bytes(op: str, M: int, N: int, K: int, world: int, elem_bytes: int = 2) -> int:
@@ -148,6 +155,9 @@ def gemm_ns(M: int, N: int, K: int, calib: Calibration, units: int | None = None
     streamed once at ``decode_gbs`` plus a fixed cost)."""
     if plain and M <= 64 and -(-N // 128) <= 2 * calib.gemm_units:
         return int(calib.decode_fixed_ns + N * K * elem_bytes / calib.decode_gbs)
+    if plain and M <= 128 and -(-N // 256) * 2 <= 2 * calib.gemm_units:
+        # one row block on the general kernel: narrow tiles or wide pieces, weights streamed once
+        return int(calib.row_block_fixed_ns + N * K * elem_bytes / calib.row_block_gbs)
     units = calib.gemm_units if units is None else max(units, 1)
     tiles = -(-M // 256) * -(-N // 256)
     k_blocks = -(-K * elem_bytes // 128)

@@ -56,7 +56,9 @@ class TPLinearSpec:
 
 
 # ---------------------------------------------------------------- candidates
-AG_PUSHER_CTAS = (4, 8, 16, 24, 32)
+# (4 pusher CTAs were a candidate once: they deliver a shard just in time on paper and 20-30 % late
+# in every measurement)
+AG_PUSHER_CTAS = (8, 16, 24, 32)
 AG_CHUNKS = (1, 2, 4, 8)
 ONE_SHOT_MAX_BYTES = 4 << 20   # partial [M, N] above which a one-shot all-reduce is not even scored
 
@@ -241,8 +243,9 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
         return plan.build(common)
 
     if sched.one_shot:
-        # plain GEMM, second launch, one flag round trip, then W-1 remote reads of the whole partial
-        setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew, stream="compute")
+        # plain GEMM (its fixed cost covers the launch), second launch, one flag round trip, then W-1
+        # remote reads of the whole partial; the ranks' launches drift apart by about half the skew
+        setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, skew // 2, stream="compute")
         g = plan.add("compute", "gemm", irops.COMPUTE_GEMM, gemm_ns(spec.M, spec.N, spec.K, calib, plain=True),
                      stream="compute", after=setup, attrs=dict(attrs))
         flag = plan.add("other", "flags", irops.EVENT_RECORD, calib.one_shot_sync_ns, deps=(g,), stream="push.flags")
