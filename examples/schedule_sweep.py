@@ -6,7 +6,7 @@ the link probe on the ranks of one box, each next to the cost model's prediction
 
 Shapes: the Llama-3-70B layer at TP=8-local extents and 8192 tokens (qkv, gate_up: all-gather +
 GEMM; o_proj, down: GEMM + reduce-scatter) and the Llama-3-8B down_proj with all-reduce at
-1..8192 tokens.  Prints one JSON line per measurement on rank 0 (CUDA events, maximum over ranks)
+1..8192 tokens (fused kernel, one-shot schedule, this library's GEMM + the library all-reduce).  Prints one JSON line per measurement on rank 0 (CUDA events, maximum over ranks)
 and writes them to ``out/sweep_tp<W>.json``.  The figures calibrate
 ``edmir_b200/calibration_b200.json``.
 """
@@ -52,11 +52,13 @@ for name, K, N in (("qkv", 8192, 1280), ("gate_up", 8192, 7168)):
     spec = lowering.TPLinearSpec("ag_gemm", M, N, K, world)
     sel = lowering.select_schedule(spec, calib)
     cands = []
-    for p in (4, 8, 16, 24, 32, 48):
-        for c in (1, 4):
+    for p in (8, 12, 16, 24, 32):
+        for c in (1, 2, 4):
             cands.append(Schedule(chunks=c, transport="sm", pusher_ctas=p))
     cands += [Schedule(chunks=2, transport="sm", pusher_ctas=0), Schedule(chunks=1, transport="ce", side_streams=2),
-              Schedule(chunks=4, transport="ce", side_streams=2), Schedule(chunks=2, transport="ce", side_streams=1)]
+              Schedule(chunks=4, transport="ce", side_streams=2), Schedule(chunks=2, transport="ce", side_streams=2),
+              Schedule(chunks=2, transport="cs", side_streams=2), Schedule(chunks=4, transport="cs", side_streams=2),
+              Schedule(chunks=4, transport="cs", side_streams=4), Schedule(chunks=8, transport="cs", side_streams=2)]
     if world > 2:
         far = (world - 1) // 2
         cands += [Schedule(chunks=4, transport="hybrid", pusher_ctas=8, ce_peers=far, side_streams=1),
@@ -82,20 +84,23 @@ for name, K, N in (("o_proj", 1024, 8192), ("down", 3584, 8192)):
     def unf():
         torch.matmul(a, b.t(), out=full); dist.reduce_scatter_tensor(out, full)
     emit(op=name, sched="unfused_nccl", us=round(timed(unf), 1))
-# ---- all-reduce (8B down_proj)
-ar_out = ctx.empty((8192, 4096), torch.bfloat16)
-for m in (1, 16, 128, 1024, 8192):
-    K, N = 14336 // world, 4096
+# ---- all-reduce (8B down_proj): fused kernel, one-shot (where it is a candidate), GEMM + library all-reduce
+K, N = 14336 // world, 4096
+w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+for m in (1, 16, 128, 512, 1024, 8192):
     a = torch.randn(m, K, device=dev).bfloat16()
-    b = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
-    part = torch.empty(m, N, device=dev, dtype=torch.bfloat16)
+    o_sym = ctx.empty((m, N), torch.bfloat16)
+    o_any = torch.empty(m, N, device=dev, dtype=torch.bfloat16)
     spec = lowering.TPLinearSpec("gemm_ar", m, N, K, world)
-    sel = lowering.select_schedule(spec, calib)
-    emit(op=f"ar_m{m}", sched="fused", us=round(timed(lambda: ctx.gemm_ar(a, b, ar_out[:m])), 1), model_us=round(sel.predicted_us, 1))
+    for s in (c for c in lowering.candidates(spec) if c.fused):
+        us = timed(lambda: ctx.gemm_ar(a, w, o_any if s.one_shot else o_sym, schedule=s), iters=30)
+        g = lowering.schedule_graph(spec, s, calib)
+        emit(op=f"ar_m{m}", sched=s.label(), us=round(us, 1), model_us=round(lowering.graph_cost(g).makespan / 1e3, 1))
     def unf():
-        torch.matmul(a, b.t(), out=part); dist.all_reduce(part)
-    emit(op=f"ar_m{m}", sched="unfused_nccl", us=round(timed(unf), 1))
-    emit(op=f"ar_m{m}", sched="gemm_only", us=round(timed(lambda: linear.gemm(a, b, part)), 1))
+        linear.gemm(a, w, o_any); dist.all_reduce(o_any)
+    emit(op=f"ar_m{m}", sched="unfused", us=round(timed(unf, iters=30), 1))
+    emit(op=f"ar_m{m}", sched="gemm_only", us=round(timed(lambda: linear.gemm(a, w, o_any), iters=30), 1))
+    ctx.reset_heap()
 # ---- link probe: one peer and all peers
 for mode in (0, 1, 2, 3):
     nbytes = 64 << 20
