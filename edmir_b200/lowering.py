@@ -95,8 +95,9 @@ def candidates(spec: TPLinearSpec, include_unfused: bool = True) -> list[Schedul
             # (one side stream delivers in consumption order but at ~60 % of the rate of two, and
             # measured slower on every shape: not a candidate)
             out.append(Schedule(chunks=c, transport="ce", side_streams=2))
-            if c >= 2:
-                out.append(Schedule(chunks=c, transport="cs", side_streams=2))
+            # (the striped copy-engine transport "cs" -- a stream per chunk, all engines on one peer at
+            # a time -- can be asked for but is not a candidate: 314-477 us against 297 us for a stream
+            # per peer on the qkv shape at 8 ranks, never ahead at 2 or 4)
         if spec.world > 2:
             for c in chunk_ok[1:3]:
                 for p in (8, 16):
@@ -261,7 +262,8 @@ def schedule_graph(spec: TPLinearSpec, sched: Schedule, calib: Calibration, tp_r
     G = min(8, rounds)
     total = gemm_ns(spec.M, spec.N, spec.K, calib)
     push_bytes = wire if spec.op == "gemm_rs" else wire // 2
-    setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew, stream="compute")
+    # (a rank only waits for peers' tiles at the very end: about half the drift of the launches shows)
+    setup = plan.add("other", "launch", irops.RUNTIME_LAUNCH_GAP, calib.launch_ns + skew // 2, stream="compute")
     g_prev, m_prev = setup, None
     for i in range(G):
         g_prev = plan.add("compute", f"gemm.{i}", irops.COMPUTE_GEMM, total // G + (1 if i < total % G else 0),

@@ -1,6 +1,6 @@
 """Times decode-sized GEMMs (a few tokens against a weight matrix) on one GPU.
 
-    python examples/decode_gemm.py [--n 4096] [--k 1792,3584,7168,14336] [--tokens 1,16,32,64,128]
+    python examples/decode_gemm.py [--n 4096] [--k 1792,3584,7168,14336] [--tokens 1,16,32,64,128] [--graph]
     EDM_DECODE=0 python examples/decode_gemm.py      # the same shapes through the general kernel
 
 Default shapes: the Llama-3-8B-shaped down_proj (N = 4096) with K = 14336 / TP for TP = 8, 4, 2, 1.
@@ -8,7 +8,9 @@ Prints one JSON line per shape: microseconds per call in a loop of back-to-back 
 events) that rotates over enough copies of the weights (>= 256 MB in total) that no launch finds
 them in the 126 MB L2, what ``torch.matmul`` takes in the same loop, the launch plan, the fraction
 of the HBM roofline (weights read once at the measured copy bandwidth) and the rel-L2 against an
-fp32 matmul.
+fp32 matmul.  ``--graph`` also replays a CUDA graph of 24 captured launches (same rotation), which
+takes the host's issue rate out of the figure (launches of up to 64 rows use no global scratch
+and can be captured).
 """
 from __future__ import annotations
 
@@ -42,6 +44,7 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", default="1792,3584,7168,14336")
     ap.add_argument("--tokens", default="1,16,32,64,128")
+    ap.add_argument("--graph", action="store_true")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     hbm_gbs = 6546.0
@@ -65,12 +68,28 @@ def main() -> None:
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             us = timed(lambda: linear.gemm(a, next_w(), out))
             lib = timed(lambda: torch.matmul(a, next_w().t(), out=out))
+            graph_us = lib_graph_us = None
+            if args.graph:
+                def replayed(call):
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        call()
+                        torch.cuda.synchronize()
+                        with torch.cuda.graph(g, stream=side):
+                            for _ in range(24):
+                                call()
+                    torch.cuda.synchronize()
+                    return timed(g.replay, iters=10, warm=2) / 24
+                graph_us = round(replayed(lambda: linear.gemm(a, next_w(), out)), 1)
+                lib_graph_us = round(replayed(lambda: torch.matmul(a, next_w().t(), out=out)), 1)
             linear.gemm(a, w, out)
             ref = torch.matmul(a.float(), w.float().t())
             err = float((out.float() - ref).norm() / ref.norm())
             roof_us = 2.0 * (M * K + N * K + M * N) / (hbm_gbs * 1e3)
             print(json.dumps({"tokens": M, "N": N, "K": K, "us": round(us, 1), "torch_matmul_us": round(lib, 1),
-                              "weight_copies": len(ws), "plan": linear.gemm_plan(M, N, K), "hbm_roofline_us": round(roof_us, 1),
+                              "graph_us": graph_us, "torch_matmul_graph_us": lib_graph_us, "weight_copies": len(ws), "plan": linear.gemm_plan(M, N, K), "hbm_roofline_us": round(roof_us, 1),
                               "roofline_frac": round(roof_us / us, 3), "rel_l2": float(f"{err:.2e}")}), flush=True)
     assert linear.status()[0] == 0, linear.status()[:8]
 

@@ -42,8 +42,7 @@ def test_candidates():
     assert not scheds[0].fused and all(s.fused for s in scheds[1:])
     # a fused one-chunk schedule exists and is not the unfused one
     assert any(s.fused and s.chunks == 1 for s in scheds)
-    assert {s.transport for s in scheds[1:]} == {"sm", "ce", "hybrid", "cs"}
-    assert all(s.chunks >= 2 for s in scheds if s.transport == "cs")
+    assert {s.transport for s in scheds[1:]} == {"sm", "ce", "hybrid"}
     assert {s.pusher_ctas for s in scheds if s.transport == "sm"} == {0, 8, 16, 24, 32}
     # two-row shards cannot be cut into more than two chunks; two ranks have no far peers
     tiny = lowering.candidates(lowering.TPLinearSpec("ag_gemm", 16, 64, 64, 8))
