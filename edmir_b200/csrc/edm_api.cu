@@ -502,12 +502,31 @@ int decode_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, void* d,
   }
   dbg_reset();
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles * split); cfg.blockDim = dim3(kDecThreads); cfg.dynamicSmemBytes = kDecSmemBytes;
+  cfg.blockDim = dim3(kDecThreads); cfg.dynamicSmemBytes = kDecSmemBytes;
   cfg.stream = s;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = split; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
+  // Every cluster must be resident at once or the launch runs in waves (a cluster needs `split`
+  // free SMs inside one GPC; with one CTA per SM not every split that fits by SM count fits by
+  // cluster count).  Clusters that can be active per (variant, split), asked once per device.
+  static std::atomic<int> active[kMaxDevices][2][4] = {};
+  for (; split > 1; split /= 2) {
+    const int si = split == 2 ? 1 : (split == 4 ? 2 : 3);
+    std::atomic<int>& slot = active[dev][tok == 32 ? 0 : 1][si];
+    int n = slot.load(std::memory_order_acquire);
+    if (n == 0) {
+      cfg.gridDim = dim3(tiles * split);
+      at[0].val.clusterDim.x = split;
+      if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = -1; }
+      slot.store(n, std::memory_order_release);
+    }
+    if (n < 0 || tiles <= n) break;  // (unknown: keep the planned split)
+  }
+  p.split = split;
+  cfg.gridDim = dim3(tiles * split);
+  at[0].val.clusterDim.x = split;
   void* args[1] = {&p};
   EDM_CUDA(cudaLaunchKernelExC(&cfg, fn, args));
   return EDM_OK;
