@@ -42,6 +42,7 @@ struct DecodeParams {
   int32_t M, N, K;
   int32_t split;       // pieces of K = CTAs per cluster (1, 2, 4 or 8; at most DecodeShape::kMaxSplit)
   uint64_t timeout_ns;
+  int32_t profile;     // accumulate per-CTA times into the profile slots (kernel, accumulator wait, epilogue)
 };
 
 __device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
@@ -64,6 +65,9 @@ decode_gemm_kernel(const __grid_constant__ DecodeParams p) {
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool prof = p.profile != 0;
+  ProfTimer prof_kernel(prof && threadIdx.x == 0);
+  ProfTimer prof_acc(prof && threadIdx.x == 64);   // first epilogue warp: launch to accumulator complete
   const int split = p.split;
   const int tile = blockIdx.x / split;
   const int piece = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
@@ -140,6 +144,8 @@ decode_gemm_kernel(const __grid_constant__ DecodeParams p) {
     }
   }
   __syncwarp();
+  prof_acc.stop(kProfEpiTmemWait);
+  ProfTimer prof_epi(prof && threadIdx.x == 64);
 
   const int q = warp & 3;             // TMEM lane quarter of an epilogue warp (warps 2..5 -> 2, 3, 0, 1)
   const int row = q * 32 + lane;      // weight row within the tile = TMEM lane
@@ -191,12 +197,15 @@ decode_gemm_kernel(const __grid_constant__ DecodeParams p) {
     }
   }
 
+  prof_epi.stop(kProfEpiTotal);
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kDecTok);
   }
+  prof_kernel.stop(kProfKernelTotal);
+  if (prof && threadIdx.x == 0) atomicAdd(&g_prof[kProfCtas], 1ull);
 }
 
 }  // namespace edm

@@ -491,6 +491,7 @@ int decode_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, void* d,
   p.M = static_cast<int32_t>(M); p.N = static_cast<int32_t>(N); p.K = static_cast<int32_t>(K);
   p.split = split;
   p.timeout_ns = g_timeout_ns;
+  p.profile = g_profile;
   void* fn = tok == 32 ? reinterpret_cast<void*>(decode_gemm_kernel<32>) : reinterpret_cast<void*>(decode_gemm_kernel<64>);
   static std::atomic<bool> configured[kMaxDevices][2] = {};
   const int dev = current_device();
