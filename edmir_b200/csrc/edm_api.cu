@@ -1513,8 +1513,10 @@ int moe_forward_impl(edm_comm_t* const* comms, const edm_moe_call_t* calls, int 
   if (sms <= 0) return EDM_ERR_CUDA;
   const dim3 wide(static_cast<unsigned>(sms / n > 0 ? sms / n : 1), static_cast<unsigned>(n));
   const dim3 one(1, static_cast<unsigned>(n));
+  // the row-copy and elementwise stages are latency-bound per warp: two to four CTAs per SM
+  const dim3 wide2(wide.x * 2, wide.y), wide4(wide.x * 4, wide.y);
   moe_route_kernel<<<one, kMoeRouteThreads, 0, s>>>(mp);
-  moe_dispatch_kernel<<<wide, 256, 0, s>>>(mp);
+  moe_dispatch_kernel<<<wide2, 256, 0, s>>>(mp);
   moe_plan_kernel<<<one, 64, 0, s>>>(mp);
   EDM_CUDA(cudaGetLastError());
   for (int i = 0; i < n; ++i) {
@@ -1524,7 +1526,7 @@ int moe_forward_impl(edm_comm_t* const* comms, const edm_moe_call_t* calls, int 
                           const_cast<__nv_bfloat16*>(R.Y), 2 * R.F, 2 * R.F, R.H, R.table_gu, R.n_blocks, R.max_blocks, s);
     if (rc) return rc;
   }
-  moe_silu_mul_kernel<<<wide, 256, 0, s>>>(mp);
+  moe_silu_mul_kernel<<<wide4, 256, 0, s>>>(mp);
   EDM_CUDA(cudaGetLastError());
   for (int i = 0; i < n; ++i) {
     const MoeRank& R = mp.r[i];
@@ -1533,8 +1535,8 @@ int moe_forward_impl(edm_comm_t* const* comms, const edm_moe_call_t* calls, int 
                           const_cast<__nv_bfloat16*>(R.Z), R.H, R.H, R.F, R.table_dn, R.n_blocks, R.max_blocks, s);
     if (rc) return rc;
   }
-  moe_combine_kernel<<<wide, 256, 0, s>>>(mp);
-  moe_finish_kernel<<<wide, 256, 0, s>>>(mp);
+  moe_combine_kernel<<<wide2, 256, 0, s>>>(mp);
+  moe_finish_kernel<<<wide4, 256, 0, s>>>(mp);
   EDM_CUDA(cudaGetLastError());
   for (int i = 0; i < n; ++i) comms[i]->epoch += 1;
   return EDM_OK;

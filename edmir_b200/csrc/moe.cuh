@@ -254,20 +254,38 @@ __global__ void __launch_bounds__(256) moe_silu_mul_kernel(const __grid_constant
   for (int q = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); q < total; q += warps) {
     int64_t row;
     if (!moe_row_of(R, q, row)) continue;
+    const int row_bytes = R.F * 2;
     const char* y = reinterpret_cast<const char*>(R.Y) + row * (2 * R.F) * 2;
     char* a = reinterpret_cast<char*>(R.act) + row * R.F * 2;
-    for (int v = lane * 16; v < R.F * 2; v += 32 * 16) {
-      const uint4 g = ld_cg_v4(y + v), u = ld_cg_v4(y + R.F * 2 + v);
-      const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
-      uint32_t ow[4];
+    // a pure HBM pass (3 F elements per row): eight 16-byte loads per lane are in flight before
+    // any is used -- with two the kernel ran at a quarter of the copy bandwidth
+    constexpr int kU = 4;
+    for (int v0 = lane * 16; v0 < row_bytes; v0 += 32 * 16 * kU) {
+      uint4 g[kU], u[kU];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xFFFF0000u);
-        const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xFFFF0000u);
-        const __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
-        ow[k] = *reinterpret_cast<const uint32_t*>(&o);
+      for (int j = 0; j < kU; ++j) {
+        const int v = v0 + j * 32 * 16;
+        if (v < row_bytes) {
+          g[j] = ld_cg_v4(y + v);
+          u[j] = ld_cg_v4(y + row_bytes + v);
+        }
       }
-      st_global_v4(a + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+#pragma unroll
+      for (int j = 0; j < kU; ++j) {
+        const int v = v0 + j * 32 * 16;
+        if (v < row_bytes) {
+          const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w}, uw[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xFFFF0000u);
+            const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xFFFF0000u);
+            const __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+            ow[k] = *reinterpret_cast<const uint32_t*>(&o);
+          }
+          st_global_v4(a + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+      }
     }
   }
 }
