@@ -272,7 +272,8 @@ struct TileWalk {
   int mb_per_rank;  // RS / AG-rotated: row blocks per rank, 0 if rows do not split on block edges
   int band;         // row blocks per band of the walk
   int band_cols;    // column blocks per super-tile of a band (0: the whole width)
-  int ag_head_blocks, ag_head_band;  // all-gather: the first row blocks are walked in lower bands
+  int ag_own_blocks;                 // all-gather: the own shard is a band of its own (nothing of it has to arrive)
+  int ag_head_blocks, ag_head_band;  // all-gather: the next row blocks are walked in lower bands
   int rounds;       // RS/AR: rounds of the owner round-robin (= most tiles any rank owns)
   int defer;        // RS/AR: own tiles of the last `defer` rounds are computed at the very end
 
@@ -292,13 +293,20 @@ struct TileWalk {
     mb_per_rank = (world > 1 && rows_per_rank * world == M && rows_per_rank % tile_m == 0)
                       ? rows_per_rank / tile_m : 0;
     // all-gather: shards arrive one after the other, about twice as fast as they are consumed.
-    // A band must not reach further ahead than what has arrived when its first wave starts: two
-    // shards per band over the first four shards, then the full band height.
+    // A band must not reach further ahead than what has arrived when its first wave starts.  At
+    // the start nothing has: the own shard is a band of its own (a band is walked column by
+    // column, so a first band of own + next shard would put half of the first wave on rows that
+    // are still on the wire).  Then two shards per band over the next four shards, then the full
+    // band height.
+    ag_own_blocks = 0;
     ag_head_blocks = 0;
     ag_head_band = band;
-    if (mode == kAG && mb_per_rank > 0 && band_rows <= 0 && 2 * mb_per_rank < band) {
-      ag_head_blocks = min(m_blocks, 4 * mb_per_rank);
-      ag_head_band = 2 * mb_per_rank;
+    if (mode == kAG && mb_per_rank > 0 && band_rows <= 0) {
+      if (mb_per_rank < band) ag_own_blocks = mb_per_rank;
+      if (2 * mb_per_rank < band) {
+        ag_head_blocks = min(m_blocks - ag_own_blocks, 4 * mb_per_rank);
+        ag_head_band = 2 * mb_per_rank;
+      }
     }
     positions = (mode == kAR && world > 1) ? (total + world - 1) / world * world : total;
     rounds = world > 1 ? positions / world : 0;
@@ -355,12 +363,16 @@ struct TileWalk {
       owned_tile(t.owner, round, t.m_blk, t.n_blk);
     } else if (mode == kAG && mb_per_rank > 0) {
       int pm, n;
+      const int own_tiles = ag_own_blocks * n_blocks;
       const int head_tiles = ag_head_blocks * n_blocks;
-      if (i < head_tiles) {
-        band_order(i, ag_head_blocks, n_blocks, pm, n, ag_head_band);
+      if (i < own_tiles) {
+        band_order(i, ag_own_blocks, n_blocks, pm, n, ag_own_blocks);
+      } else if (i < own_tiles + head_tiles) {
+        band_order(i - own_tiles, ag_head_blocks, n_blocks, pm, n, ag_head_band);
+        pm += ag_own_blocks;
       } else {
-        band_order(i - head_tiles, m_blocks - ag_head_blocks, n_blocks, pm, n, band, band_cols);
-        pm += ag_head_blocks;
+        band_order(i - own_tiles - head_tiles, m_blocks - ag_own_blocks - ag_head_blocks, n_blocks, pm, n, band, band_cols);
+        pm += ag_own_blocks + ag_head_blocks;
       }
       t.m_blk = (rank * mb_per_rank + pm) % m_blocks;  // own shard first, then rank+1, ...
       t.n_blk = n;

@@ -87,6 +87,11 @@ def test_all_gather_walk_follows_arrival_order(native_lib, world):
         walk = symm.tile_walk("ag_gemm", rank, world, M, N, tile_m, 256, 0, 74)
         shard_of = [((m - rank * per_rank) % (M // tile_m)) // per_rank for m, _, _, _ in walk]
         assert all(s == 0 for s in shard_of[:min(per_rank, 16)])      # first tiles: own rows
+        if per_rank < 16:
+            # a shard shorter than a band is a band of its own: every tile of the own shard comes
+            # before any tile whose rows have to arrive first
+            own = per_rank * (N // 256)
+            assert all(s == 0 for s in shard_of[:own]) and shard_of[own] == 1
         # position of the first tile of shard s (in arrival order s = 0 own, 1 = rank+1, ...)
         first = {s: shard_of.index(s) for s in range(world)}
         assert [first[s] for s in range(world)] == sorted(first.values())
